@@ -1,0 +1,135 @@
+"""ctypes binding of ``libheddle_b200.so`` (the C ABI declared in include/heddle_b200.h).
+
+There is deliberately no fallback: if the library is missing or a call fails, a
+``RuntimeError`` carrying ``hb_last_error()`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+_PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = _PKG_DIR / "libheddle_b200.so"
+
+HB_OK = 0
+HB_ERR_BAD_ARG = 1
+HB_ERR_UNSUPPORTED = 2
+HB_ERR_ALIGN = 3
+HB_ERR_CUDA = 4
+HB_ERR_TIMEOUT = 5
+
+HB_BF16 = 0
+HB_FP16 = 1
+HB_FP8_E4M3 = 2
+
+HB_QUERY_SM_COUNT = 0
+HB_QUERY_SMEM_OPTIN = 1
+HB_QUERY_CC = 2
+HB_QUERY_FA_SMEM = 3
+HB_QUERY_GEMM_SMEM = 4
+
+EPILOGUES = {
+    "none": 0, "silu": 1, "relu": 2, "gelu_tanh": 3, "sigmoid": 4, "tanh": 5, "swiglu": 6, "rope": 7,
+}
+
+
+class FaArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Sq", C.c_int32), ("Skv", C.c_int32),
+        ("D", C.c_int32),
+        ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64), ("q_stride_s", C.c_int64),
+        ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64), ("k_stride_s", C.c_int64),
+        ("v_stride_b", C.c_int64), ("v_stride_h", C.c_int64), ("v_stride_s", C.c_int64),
+        ("o_stride_b", C.c_int64), ("o_stride_h", C.c_int64), ("o_stride_s", C.c_int64),
+        ("causal", C.c_int32), ("softmax_scale", C.c_float), ("dtype", C.c_int32),
+        ("q_scale", C.c_float), ("k_scale", C.c_float), ("v_scale", C.c_float), ("p_scale", C.c_float),
+        ("o_scale", C.c_float),
+        ("stream", C.c_void_p),
+    ]
+
+
+class H2oArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("lse", C.c_void_p), ("score", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Sq", C.c_int32), ("Skv", C.c_int32),
+        ("D", C.c_int32),
+        ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64), ("q_stride_s", C.c_int64),
+        ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64), ("k_stride_s", C.c_int64),
+        ("causal", C.c_int32), ("softmax_scale", C.c_float), ("dtype", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p),
+        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+        ("lda", C.c_int64), ("ldw", C.c_int64), ("ldo", C.c_int64),
+        ("dtype", C.c_int32), ("epilogue", C.c_int32),
+        ("row_scale", C.c_void_p), ("residual", C.c_void_p), ("ldr", C.c_int64),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("rope_seq", C.c_int32), ("head_dim", C.c_int32), ("rope_cols", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
+# every symbol include/heddle_b200.h declares
+EXPORTS = (
+    "hb_fa_fwd", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_status_word", "hb_version",
+    "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma",
+)
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = Path(os.environ.get("HEDDLE_B200_LIB", str(LIB_PATH)))
+    if not path.exists():
+        raise RuntimeError(
+            f"{path} not found: build it with `python -m heddle_b200._build` "
+            "(there is no CPU or PyTorch fallback for the heddle_b200 kernels)")
+    lib = C.CDLL(str(path))
+    lib.hb_fa_fwd.argtypes = [C.POINTER(FaArgs)]
+    lib.hb_fa_fwd.restype = C.c_int
+    lib.hb_h2o_score.argtypes = [C.POINTER(H2oArgs)]
+    lib.hb_h2o_score.restype = C.c_int
+    lib.hb_gemm_epilogue.argtypes = [C.POINTER(GemmArgs)]
+    lib.hb_gemm_epilogue.restype = C.c_int
+    lib.hb_rms_rowstat.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                   C.c_int64, C.c_float, C.c_int32, C.c_void_p]
+    lib.hb_rms_rowstat.restype = C.c_int
+    lib.hb_status_word.argtypes = [C.POINTER(C.c_uint32)]
+    lib.hb_status_word.restype = C.c_int
+    lib.hb_version.argtypes = []
+    lib.hb_version.restype = C.c_int
+    lib.hb_query.argtypes = [C.c_int]
+    lib.hb_query.restype = C.c_int
+    lib.hb_last_error.argtypes = []
+    lib.hb_last_error.restype = C.c_char_p
+    lib.hb_shutdown.argtypes = []
+    lib.hb_shutdown.restype = C.c_int
+    lib.hb_debug_umma.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+    lib.hb_debug_umma.restype = C.c_int
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().hb_last_error().decode("utf-8", "replace")
+
+
+class HeddleError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"heddle_b200 error {code}: {message}")
+        self.code = code
+
+
+def check(rc: int) -> None:
+    if rc != HB_OK:
+        raise HeddleError(rc, last_error())

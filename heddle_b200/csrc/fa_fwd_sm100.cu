@@ -1,0 +1,288 @@
+// hb_fa_fwd: argument validation, TMA descriptors and launch of the sm_100a
+// FlashAttention-forward kernel; plus hb_debug_umma, a one-tile tcgen05 probe that
+// goes through the same descriptor helpers.
+#include "fa_fwd_sm100.cuh"
+#include "host_common.h"
+
+#include <algorithm>
+#include <cmath>
+
+namespace hb {
+
+template <int D>
+struct FaConfig;
+template <>
+struct FaConfig<128> {
+  static constexpr int kStages = 5;
+};
+template <>
+struct FaConfig<64> {
+  static constexpr int kStages = 8;
+};
+
+template <typename T, int D>
+static int launch_fa(const FaParams& p, int grid, int smem_optin, cudaStream_t stream) {
+  constexpr int NS = FaConfig<D>::kStages;
+  using Smem = FaSmem<D, NS>;
+  if ((int)sizeof(Smem) > smem_optin)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: kernel needs %d bytes of shared memory, device offers %d",
+                     (int)sizeof(Smem), smem_optin);
+  auto kernel = fa_fwd_kernel<T, D, NS>;
+  static bool configured[64] = {};
+  int dev = 0;
+  HB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+    configured[dev & 63] = true;
+  }
+  kernel<<<grid, kFaThreads, sizeof(Smem), stream>>>(p);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB_OK;
+}
+
+static int fa_fwd_impl(const hb_fa_args* a) {
+  if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: args is NULL");
+  if (a->B < 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq < 0 || a->Skv < 0 || a->D <= 0)
+    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: negative or zero extent (B=%d Hq=%d Hkv=%d Sq=%d Skv=%d D=%d)", a->B,
+                     a->Hq, a->Hkv, a->Sq, a->Skv, a->D);
+  if (a->Hq % a->Hkv != 0)
+    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
+  if (a->dtype != HB_BF16 && a->dtype != HB_FP16 && a->dtype != HB_FP8_E4M3)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: unknown dtype %d", a->dtype);
+  if (a->dtype == HB_FP8_E4M3) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: FP8 path not built yet");
+  if (a->D != 64 && a->D != 128)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: head_dim %d not supported (64 or 128)", a->D);
+  if (a->B == 0 || a->Sq == 0) return HB_OK;  // nothing to compute
+  if (a->Skv == 0) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: Skv is 0 (softmax over an empty set)");
+  if (a->causal && a->Skv < a->Sq)
+    return set_error(HB_ERR_UNSUPPORTED,
+                     "hb_fa_fwd: causal attention needs Skv >= Sq (the reference asserts past_len >= 0)");
+  if (a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr)
+    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: q, k, v and o must be non-NULL");
+  const size_t es = dtype_size(a->dtype);
+  if ((reinterpret_cast<uintptr_t>(a->o) & 15u) != 0 || ((a->o_stride_s * es) & 15u) != 0 ||
+      ((a->o_stride_h * es) & 15u) != 0 || ((a->o_stride_b * es) & 15u) != 0)
+    return set_error(HB_ERR_ALIGN, "hb_fa_fwd: o and its strides must be 16-byte aligned");
+  if (a->lse != nullptr && (reinterpret_cast<uintptr_t>(a->lse) & 3u) != 0)
+    return set_error(HB_ERR_ALIGN, "hb_fa_fwd: lse must be 4-byte aligned");
+
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != HB_OK) return rc;
+
+  FaParams p;
+  memset(&p, 0, sizeof(p));
+  const CUtensorMapDataType dt =
+      a->dtype == HB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const uint32_t box[4] = {64, (uint32_t)kTileM, 1, 1};
+  {
+    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Sq, (uint64_t)a->Hq, (uint64_t)a->B};
+    const uint64_t str[3] = {(uint64_t)a->q_stride_s * es, (uint64_t)a->q_stride_h * es, (uint64_t)a->q_stride_b * es};
+    rc = encode_tensor_map(&p.tm_q, dt, 4, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  }
+  {
+    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Skv, (uint64_t)a->Hkv, (uint64_t)a->B};
+    const uint64_t str[3] = {(uint64_t)a->k_stride_s * es, (uint64_t)a->k_stride_h * es, (uint64_t)a->k_stride_b * es};
+    rc = encode_tensor_map(&p.tm_k, dt, 4, a->k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  }
+  {
+    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Skv, (uint64_t)a->Hkv, (uint64_t)a->B};
+    const uint64_t str[3] = {(uint64_t)a->v_stride_s * es, (uint64_t)a->v_stride_h * es, (uint64_t)a->v_stride_b * es};
+    rc = encode_tensor_map(&p.tm_v, dt, 4, a->v, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  }
+  p.o = a->o;
+  p.lse = a->lse;
+  p.status = st->status_word;
+  p.o_sb = a->o_stride_b;
+  p.o_sh = a->o_stride_h;
+  p.o_ss = a->o_stride_s;
+  p.B = a->B;
+  p.Hq = a->Hq;
+  p.Hkv = a->Hkv;
+  p.Sq = a->Sq;
+  p.Skv = a->Skv;
+  p.group = a->Hq / a->Hkv;
+  p.causal = a->causal ? 1 : 0;
+  p.nqb = (a->Sq + 2 * kTileM - 1) / (2 * kTileM);
+  p.npairs = (p.nqb + 1) / 2;
+  const long long total = (long long)a->B * a->Hq * p.npairs;
+  if (total > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: problem too large (%lld blocks)", total);
+  p.total_pairs = (int)total;
+  p.nkv = (a->Skv + kTileN - 1) / kTileN;
+  const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->D);
+  p.scale_log2 = scale * 1.4426950408889634f;
+
+  const int grid = (int)std::min<long long>(total, st->sm_count);
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (a->dtype == HB_BF16) {
+    return a->D == 128 ? launch_fa<__nv_bfloat16, 128>(p, grid, st->smem_optin, stream) : launch_fa<__nv_bfloat16, 64>(p, grid, st->smem_optin, stream);
+  }
+  return a->D == 128 ? launch_fa<__half, 128>(p, grid, st->smem_optin, stream) : launch_fa<__half, 64>(p, grid, st->smem_optin, stream);
+}
+
+// ------------------------------------------------------------------------------------
+// one-tile tcgen05 probe
+// ------------------------------------------------------------------------------------
+struct alignas(64) UmmaProbeParams {
+  CUtensorMap tm_a;  // mode 0: A [128, K];  mode 1: unused
+  CUtensorMap tm_b;  // mode 0: B [128, K];  mode 1: V [128, N]
+  const uint32_t* p_packed;  // mode 1: P [128,128] 16-bit, row-major (64 words per row)
+  float* out;
+  uint32_t* status;
+  int mode, kn, fmt;
+};
+
+struct UmmaProbeSmem {
+  alignas(1024) uint8_t a[32768];
+  alignas(1024) uint8_t b[32768];
+  uint64_t full, done;
+  uint32_t tmem_base, abort_flag;
+};
+
+__global__ void __launch_bounds__(128, 1) umma_probe_kernel(const __grid_constant__ UmmaProbeParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  UmmaProbeSmem& s = *reinterpret_cast<UmmaProbeSmem*>(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  AbortCtx ctx{&s.abort_flag, p.status};
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.full, 1);
+    mbar_init(&s.done, 1);
+    fence_mbar_init();
+    if ((smem_u32(smem_raw) & 1023u) != 0u) raise_abort(ctx, kStatusSmemMisaligned);
+  }
+  if (warp == 0) {
+    tmem_alloc(&s.tmem_base, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+  const int halves = p.kn / 64;
+  bool ok = (s.abort_flag == 0);
+
+  if (ok && p.mode == 1) {
+    // P row of this thread -> TMEM columns [0, 64)
+    uint32_t r[64];
+#pragma unroll
+    for (int c = 0; c < 64; ++c) r[c] = p.p_packed[threadIdx.x * 64 + c];
+    tmem_st32(tmem + lane_off, &r[0]);
+    tmem_st32(tmem + lane_off + 32, &r[32]);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+
+  if (ok && threadIdx.x == 0) {
+    tc_fence_after();
+    const uint32_t bytes_b = 128u * (uint32_t)p.kn * 2u;
+    if (p.mode == 0) {
+      mbar_arrive_expect_tx(&s.full, 2 * bytes_b);
+      for (int h = 0; h < halves; ++h) {
+        tma_load_2d(s.a + h * 16384, &p.tm_a, &s.full, h * 64, 0);
+        tma_load_2d(s.b + h * 16384, &p.tm_b, &s.full, h * 64, 0);
+      }
+    } else {
+      mbar_arrive_expect_tx(&s.full, bytes_b);
+      for (int h = 0; h < halves; ++h) tma_load_2d(s.b + h * 16384, &p.tm_b, &s.full, h * 64, 0);
+    }
+    if (mbar_wait(&s.full, 0, ctx, 10)) {
+      tc_fence_after();
+      if (p.mode == 0) {
+        const uint32_t idesc = make_idesc((uint32_t)p.fmt, 128, 128, 0, 0);
+        for (int kk = 0; kk < p.kn / 16; ++kk) {
+          const uint32_t off = (uint32_t)(kk / 4) * 16384u + (uint32_t)(kk % 4) * 32u;
+          umma_ss_f16(tmem + 128, make_smem_desc_sw128(smem_u32(s.a) + off, 16, 1024),
+                      make_smem_desc_sw128(smem_u32(s.b) + off, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+        }
+      } else {
+        const uint32_t idesc = make_idesc((uint32_t)p.fmt, 128, (uint32_t)p.kn, 0, 1);
+        for (int kk = 0; kk < 8; ++kk) {
+          umma_ts_f16(tmem + 128, tmem + (uint32_t)(kk * 8),
+                      make_smem_desc_sw128(smem_u32(s.b) + (uint32_t)kk * 2048u, 16384, 1024), idesc,
+                      kk > 0 ? 1u : 0u);
+        }
+      }
+      umma_commit(&s.done);
+    }
+  }
+  __syncwarp();
+  const int ncols = p.mode == 0 ? 128 : p.kn;
+  if (ok && mbar_wait(&s.done, 0, ctx, 11)) {
+    tc_fence_after();
+    for (int c = 0; c < ncols / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tmem + lane_off + 128u + (uint32_t)(c * 32), r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) p.out[threadIdx.x * ncols + c * 32 + e] = __uint_as_float(r[e]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+static int debug_umma_impl(int mode, const void* a, const void* b, float* out, int kn, int dtype, void* stream) {
+  if (a == nullptr || b == nullptr || out == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_debug_umma: NULL pointer");
+  if (mode != 0 && mode != 1) return set_error(HB_ERR_BAD_ARG, "hb_debug_umma: mode must be 0 or 1");
+  if (kn != 64 && kn != 128) return set_error(HB_ERR_BAD_ARG, "hb_debug_umma: kn must be 64 or 128");
+  if (dtype != HB_BF16 && dtype != HB_FP16) return set_error(HB_ERR_UNSUPPORTED, "hb_debug_umma: 16-bit dtypes only");
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != HB_OK) return rc;
+  UmmaProbeParams p;
+  memset(&p, 0, sizeof(p));
+  const CUtensorMapDataType dt = dtype == HB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const uint64_t dims[2] = {(uint64_t)kn, 128};
+  const uint64_t str[1] = {(uint64_t)kn * 2};
+  const uint32_t box[2] = {64, 128};
+  if (mode == 0) {
+    rc = encode_tensor_map(&p.tm_a, dt, 2, a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  } else {
+    p.p_packed = static_cast<const uint32_t*>(a);
+  }
+  rc = encode_tensor_map(&p.tm_b, dt, 2, b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != HB_OK) return rc;
+  p.out = out;
+  p.status = st->status_word;
+  p.mode = mode;
+  p.kn = kn;
+  p.fmt = dtype == HB_BF16 ? 1 : 0;
+  static bool configured[64] = {};
+  if (!configured[st->device & 63]) {
+    HB_CUDA_CHECK(cudaFuncSetAttribute(umma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)sizeof(UmmaProbeSmem)));
+    configured[st->device & 63] = true;
+  }
+  umma_probe_kernel<<<1, 128, sizeof(UmmaProbeSmem), static_cast<cudaStream_t>(stream)>>>(p);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB_OK;
+}
+
+int fa_smem_bytes() { return (int)sizeof(FaSmem<128, FaConfig<128>::kStages>); }
+
+}  // namespace hb
+
+extern "C" {
+
+int hb_fa_fwd(const hb_fa_args* args) {
+  hb::clear_error();
+  return hb::fa_fwd_impl(args);
+}
+
+int hb_debug_umma(int mode, const void* a, const void* b, float* out, int32_t kn, int32_t dtype, void* stream) {
+  hb::clear_error();
+  return hb::debug_umma_impl(mode, a, b, out, kn, dtype, stream);
+}
+
+}  // extern "C"

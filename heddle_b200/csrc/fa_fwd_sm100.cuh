@@ -1,0 +1,537 @@
+// FlashAttention forward for sm_100a (B200): a fixed warp-specialised schedule.
+//
+// Arithmetic follows the reference template Heddle/heddle/tileop/flash_attention.py:20-143
+// (scores scaled by softmax_scale*log2(e), online row max / row sum with exp2, P
+// rounded to the input dtype before the PV product, O divided by the row sum at the
+// end) and its LSE twin (:158-300).  The Hopper pipeline the reference derives with
+// CP-SAT / TileLang passes is replaced by this schedule, per CTA (512 threads):
+//
+//   warps 0-3   softmax warpgroup for query tile 0 (128 rows, one row per thread)
+//   warps 4-7   softmax warpgroup for query tile 1
+//   warps 8-11  correction warpgroup: rescales O in TMEM when a row max moved,
+//               final O / l, LSE, conversion and the global store
+//   warp  12    MMA issuer: one thread issues tcgen05.mma for S = Q K^T (operands in
+//               shared memory) and O += P V (P read from TMEM, V MN-major in shared
+//               memory); accumulators live in TMEM
+//   warp  13    TMA producer: Q tiles and a ring of K/V tiles behind mbarriers
+//
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i is
+// written over the first 64 (16-bit) columns of S_i once the row is in registers.
+//
+// Work: a CTA handles 256 query rows of one (batch, head) at a time and walks a
+// static list of such blocks.  For causal attention block q and block (last-q) are
+// paired so that every list entry costs the same; the list is head-major so the
+// CTAs running at one time share K/V in L2.
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace hb {
+
+constexpr int kFaThreads = 512;
+constexpr int kTileM = 128;  // query rows per softmax warpgroup
+constexpr int kTileN = 128;  // keys per step
+constexpr float kRescaleThreshold = 8.0f;  // log2 units; below it the stale max is kept
+
+enum FaRole : uint32_t { kRoleSoftmax = 1, kRoleCorrection = 2, kRoleMma = 3, kRoleTma = 4, kRoleDrain = 5 };
+
+struct alignas(64) FaParams {
+  CUtensorMap tm_q;
+  CUtensorMap tm_k;
+  CUtensorMap tm_v;
+  void* o;
+  float* lse;
+  uint32_t* status;
+  long long o_sb, o_sh, o_ss;  // elements
+  int B, Hq, Hkv, Sq, Skv;
+  int group;        // Hq / Hkv
+  int causal;
+  int nqb;          // 256-row query blocks per head
+  int npairs;       // ceil(nqb / 2)
+  int total_pairs;  // B * Hq * npairs
+  int nkv;          // 128-key tiles
+  float scale_log2; // softmax_scale * log2(e)
+};
+
+template <int D, int NS>
+struct FaSmem {
+  static constexpr int kTileBytes = kTileM * D * 2;
+  alignas(1024) uint8_t q[2][kTileBytes];
+  alignas(1024) uint8_t kv[NS][kTileBytes];
+  float alpha[2][kTileM];   // per-step rescale factor; carries the final row sum at the end of a block
+  float stat_m[2][kTileM];  // final row max
+  uint64_t q_full[2], q_empty[2];
+  uint64_t kv_full[NS], kv_empty[NS];
+  uint64_t s_full[2];     // MMA -> softmax: S_i holds the scores of the next step
+  uint64_t p_full[2];     // softmax + correction -> MMA: P_i written and O_i rescaled
+  uint64_t corr_full[2];  // softmax -> correction: alpha (or final l, m) published
+  uint64_t corr_empty[2];
+  uint64_t o_full[2];     // MMA -> correction: O_i complete
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+struct FaItem {
+  int b, hq, hkv, q0;
+  int n[2];  // key tiles each query tile visits (0 = tile entirely past Sq)
+};
+
+// Entry `g` of the static work list, first (half = 0) or second block of the pair.
+__device__ __forceinline__ bool fa_get_item(const FaParams& p, int g, int half, FaItem& it) {
+  const int pair = g % p.npairs;
+  const int bh = g / p.npairs;
+  const int qb_hi = p.nqb - 1 - pair;
+  const int qb = half == 0 ? qb_hi : pair;
+  if (half == 1 && pair == qb_hi) return false;
+  it.b = bh / p.Hq;
+  it.hq = bh - it.b * p.Hq;
+  it.hkv = it.hq / p.group;
+  it.q0 = qb * (2 * kTileM);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r0 = it.q0 + kTileM * i;
+    if (r0 >= p.Sq) {
+      it.n[i] = 0;
+    } else if (p.causal) {
+      const int last = min(r0 + kTileM - 1, p.Sq - 1) + (p.Skv - p.Sq);
+      it.n[i] = min(p.nkv, last / kTileN + 1);
+    } else {
+      it.n[i] = p.nkv;
+    }
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------
+// softmax warpgroup (tile i): one query row per thread
+// ------------------------------------------------------------------------------------
+template <typename T, int D, int NS>
+__device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx,
+                                                uint32_t tmem, int i) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = threadIdx.x & (kTileM - 1);
+  const uint32_t tS = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(i * kTileN);
+  const float scale_log2 = p.scale_log2;
+  uint32_t s_cnt = 0, c_cnt = 0;
+
+  for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
+    for (int half = 0; half < 2; ++half) {
+      FaItem it;
+      if (!fa_get_item(p, g, half, it)) continue;
+      const int n = it.n[i];
+      if (n == 0) continue;
+      const int tile_pos0 = it.q0 + kTileM * i + (p.Skv - p.Sq);  // key position the first row may see up to
+      const int row_pos = tile_pos0 + row;
+      float m = -INFINITY, l = 0.f;
+
+      for (int j = 0; j < n; ++j) {
+        if (!mbar_wait_warp(&s.s_full[i], s_cnt & 1, ctx, kRoleSoftmax)) return;
+        ++s_cnt;
+        tc_fence_after();
+
+        uint32_t v[kTileN];  // fp32 scores of this row, as raw bits
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, &v[c * 32]);
+        tmem_wait_ld();
+
+        const int col0 = j * kTileN;
+        const bool need_mask = (col0 + kTileN > p.Skv) || (p.causal && (col0 + kTileN - 1 > tile_pos0));
+        if (need_mask) {
+          int lim = p.Skv - 1 - col0;
+          if (p.causal) lim = min(lim, row_pos - col0);
+#pragma unroll
+          for (int c = 0; c < kTileN; ++c) v[c] = (c <= lim) ? v[c] : 0xff800000u;  // -inf
+        }
+
+        float mx0 = __uint_as_float(v[0]), mx1 = __uint_as_float(v[1]);
+        float mx2 = __uint_as_float(v[2]), mx3 = __uint_as_float(v[3]);
+#pragma unroll
+        for (int c = 4; c < kTileN; c += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(v[c]));
+          mx1 = fmaxf(mx1, __uint_as_float(v[c + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(v[c + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(v[c + 3]));
+        }
+        const float row_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+        // New running max; a max that moved by less than the threshold is not adopted,
+        // so O needs no rescale for it (l and O stay relative to the same stale max).
+        float m_new = fmaxf(m, row_max);
+        float alpha = 1.f;
+        if (m_new != -INFINITY) {
+          const float diff = (m - m_new) * scale_log2;
+          if (diff >= -kRescaleThreshold) {
+            m_new = m;
+          } else {
+            alpha = fast_exp2(diff);
+          }
+        }
+        m = m_new;
+        const float m_scaled = (m == -INFINITY) ? 0.f : m * scale_log2;
+
+        // publish alpha for the correction warpgroup as early as possible
+        if (!mbar_wait_warp(&s.corr_empty[i], (c_cnt & 1) ^ 1, ctx, kRoleSoftmax)) return;
+        s.alpha[i][row] = alpha;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.corr_full[i]);
+        ++c_cnt;
+
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+        for (int q = 0; q < kTileN / 32; ++q) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const int c = q * 32 + e;
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), scale_log2, -m_scaled));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), scale_log2, -m_scaled));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(v[c + 2]), scale_log2, -m_scaled));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(v[c + 3]), scale_log2, -m_scaled));
+            sum0 += p0;
+            sum1 += p1;
+            sum2 += p2;
+            sum3 += p3;
+            pk[e / 2] = Pack2<T>::pack(p0, p1);
+            pk[e / 2 + 1] = Pack2<T>::pack(p2, p3);
+          }
+          tmem_st16(tS + q * 16, pk);
+        }
+        l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.p_full[i]);
+      }
+
+      // final row statistics for the epilogue
+      if (!mbar_wait_warp(&s.corr_empty[i], (c_cnt & 1) ^ 1, ctx, kRoleSoftmax)) return;
+      s.alpha[i][row] = l;
+      s.stat_m[i][row] = m;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.corr_full[i]);
+      ++c_cnt;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// correction warpgroup
+// ------------------------------------------------------------------------------------
+template <typename T, int D, int NS>
+__device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx,
+                                                   uint32_t tmem) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = threadIdx.x & (kTileM - 1);
+  const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  uint32_t c_cnt[2] = {0, 0}, o_cnt[2] = {0, 0};
+
+  for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
+    for (int half = 0; half < 2; ++half) {
+      FaItem it;
+      if (!fa_get_item(p, g, half, it)) continue;
+      const int nmax = max(it.n[0], it.n[1]);
+
+      for (int j = 0; j < nmax; ++j) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (j >= it.n[i]) continue;
+          if (!mbar_wait_warp(&s.corr_full[i], c_cnt[i] & 1, ctx, kRoleCorrection)) return;
+          ++c_cnt[i];
+          const float a = s.alpha[i][row];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.corr_empty[i]);
+          if (j > 0 && __any_sync(0xffffffffu, a != 1.f)) {
+            tc_fence_after();
+            const uint32_t tO = tmem + lane_off + 256u + static_cast<uint32_t>(i * 128);
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld32(tO + c * 32, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * a);
+              tmem_st32(tO + c * 32, r);
+            }
+            tmem_wait_st();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.p_full[i]);
+        }
+      }
+
+      // epilogue: O_i / l, LSE, convert, store
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        if (it.n[i] == 0) continue;
+        if (!mbar_wait_warp(&s.corr_full[i], c_cnt[i] & 1, ctx, kRoleCorrection)) return;
+        ++c_cnt[i];
+        const float l = s.alpha[i][row];
+        const float m = s.stat_m[i][row];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.corr_empty[i]);
+        if (!mbar_wait_warp(&s.o_full[i], o_cnt[i] & 1, ctx, kRoleCorrection)) return;
+        ++o_cnt[i];
+        tc_fence_after();
+
+        const int qrow = it.q0 + kTileM * i + row;
+        const bool live = qrow < p.Sq;
+        const float inv_l = (l > 0.f) ? (1.f / l) : 0.f;
+        T* orow = static_cast<T*>(p.o) + it.b * p.o_sb + it.hq * p.o_sh + static_cast<long long>(qrow) * p.o_ss;
+        const uint32_t tO = tmem + lane_off + 256u + static_cast<uint32_t>(i * 128);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tO + c * 32, r);
+          tmem_wait_ld();
+          if (live) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 w;
+              w.x = Pack2<T>::pack(__uint_as_float(r[e]) * inv_l, __uint_as_float(r[e + 1]) * inv_l);
+              w.y = Pack2<T>::pack(__uint_as_float(r[e + 2]) * inv_l, __uint_as_float(r[e + 3]) * inv_l);
+              w.z = Pack2<T>::pack(__uint_as_float(r[e + 4]) * inv_l, __uint_as_float(r[e + 5]) * inv_l);
+              w.w = Pack2<T>::pack(__uint_as_float(r[e + 6]) * inv_l, __uint_as_float(r[e + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
+            }
+          }
+        }
+        if (live && p.lse != nullptr) {
+          // natural-log LSE of the scaled, masked scores
+          const float lse2 = (l > 0.f) ? (m * p.scale_log2 + fast_log2(l)) : -INFINITY;
+          p.lse[(static_cast<long long>(it.b) * p.Hq + it.hq) * p.Sq + qrow] = lse2 * 0.6931471805599453f;
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// MMA issuer (one thread)
+// ------------------------------------------------------------------------------------
+template <typename T, int D, int NS>
+__device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx,
+                                            uint32_t tmem) {
+  constexpr uint32_t kFmt = Pack2<T>::kFormat;
+  constexpr uint32_t idesc_qk = make_idesc(kFmt, kTileM, kTileN, 0, 0);
+  constexpr uint32_t idesc_pv = make_idesc(kFmt, kTileM, D, 0, 1);
+  constexpr uint32_t kHalfBytes = kTileM * 128;  // one 64-element-wide, 128-row sub-tile
+  uint32_t kv_cons = 0, q_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
+
+  // Descriptor constants: only the 14-bit start-address field changes per MMA.
+  constexpr uint64_t kDescK = (uint64_t(16 >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+  constexpr uint64_t kDescV =
+      (uint64_t(kHalfBytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+  const uint32_t q_base = smem_u32(s.q[0]) >> 4;
+  const uint32_t kv_base = smem_u32(s.kv[0]) >> 4;
+  constexpr uint32_t kTile16 = FaSmem<D, NS>::kTileBytes >> 4;
+
+  auto issue_qk = [&](int i, uint32_t slot) {
+    const uint32_t qa = q_base + static_cast<uint32_t>(i) * kTile16;
+    const uint32_t ka = kv_base + slot * kTile16;
+    const uint32_t d_tmem = tmem + static_cast<uint32_t>(i * kTileN);
+#pragma unroll 1
+    for (int kk = 0; kk < D / 16; ++kk) {
+      // 16 elements (32 bytes) per step inside a 64-element sub-tile, then the next sub-tile
+      const uint32_t off = (static_cast<uint32_t>(kk >> 2) * kHalfBytes + static_cast<uint32_t>(kk & 3) * 32u) >> 4;
+      umma_ss_f16(d_tmem, kDescK | (qa + off), kDescK | (ka + off), idesc_qk, kk > 0 ? 1u : 0u);
+    }
+  };
+  auto issue_pv = [&](int i, uint32_t slot, bool accumulate) {
+    const uint32_t va = kv_base + slot * kTile16;
+    const uint32_t d_tmem = tmem + 256u + static_cast<uint32_t>(i * 128);
+    const uint32_t a_tmem = tmem + static_cast<uint32_t>(i * kTileN);
+#pragma unroll 1
+    for (int kk = 0; kk < kTileN / 16; ++kk) {
+      // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2048 bytes) of V
+      umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), kDescV | (va + static_cast<uint32_t>(kk) * 128u),
+                  idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+    }
+  };
+
+  for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
+    for (int half = 0; half < 2; ++half) {
+      FaItem it;
+      if (!fa_get_item(p, g, half, it)) continue;
+      const int nmax = max(it.n[0], it.n[1]);
+
+      // step 0 scores
+      uint32_t slot_k = kv_cons % NS;
+      if (!mbar_wait(&s.kv_full[slot_k], (kv_cons / NS) & 1, ctx, kRoleMma)) return;
+      ++kv_cons;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        if (it.n[i] == 0) continue;
+        if (!mbar_wait(&s.q_full[i], q_cnt[i] & 1, ctx, kRoleMma)) return;
+        ++q_cnt[i];
+        tc_fence_after();
+        issue_qk(i, slot_k);
+        umma_commit(&s.s_full[i]);
+        if (it.n[i] == 1) umma_commit(&s.q_empty[i]);
+      }
+      umma_commit(&s.kv_empty[slot_k]);
+
+      for (int j = 0; j < nmax; ++j) {
+        const uint32_t slot_v = kv_cons % NS;
+        if (!mbar_wait(&s.kv_full[slot_v], (kv_cons / NS) & 1, ctx, kRoleMma)) return;
+        ++kv_cons;
+        const bool has_next = (j + 1 < nmax);
+        bool k_ready = false;
+        slot_k = kv_cons % NS;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (j < it.n[i]) {
+            if (!mbar_wait(&s.p_full[i], p_cnt[i] & 1, ctx, kRoleMma)) return;
+            ++p_cnt[i];
+            tc_fence_after();
+            issue_pv(i, slot_v, j > 0);
+            if (j == it.n[i] - 1) umma_commit(&s.o_full[i]);
+          }
+          if (j + 1 < it.n[i]) {
+            if (!k_ready) {
+              if (!mbar_wait(&s.kv_full[slot_k], (kv_cons / NS) & 1, ctx, kRoleMma)) return;
+              tc_fence_after();
+              k_ready = true;
+            }
+            issue_qk(i, slot_k);
+            umma_commit(&s.s_full[i]);
+            if (j + 2 == it.n[i]) umma_commit(&s.q_empty[i]);
+          }
+        }
+        umma_commit(&s.kv_empty[slot_v]);
+        if (has_next) {
+          umma_commit(&s.kv_empty[slot_k]);
+          ++kv_cons;
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// TMA producer (one thread)
+// ------------------------------------------------------------------------------------
+template <typename T, int D, int NS>
+__device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx) {
+  constexpr uint32_t kTileBytes = FaSmem<D, NS>::kTileBytes;
+  constexpr uint32_t kHalfBytes = kTileM * 128;
+  uint32_t kv_prod = 0, q_cnt[2] = {0, 0};
+
+  for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
+    for (int half = 0; half < 2; ++half) {
+      FaItem it;
+      if (!fa_get_item(p, g, half, it)) continue;
+      const int nmax = max(it.n[0], it.n[1]);
+
+      auto load_q = [&](int i) -> bool {
+        if (!mbar_wait(&s.q_empty[i], (q_cnt[i] & 1) ^ 1, ctx, kRoleTma)) return false;
+        ++q_cnt[i];
+        mbar_arrive_expect_tx(&s.q_full[i], kTileBytes);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_4d(s.q[i] + h * kHalfBytes, &p.tm_q, &s.q_full[i], h * 64, it.q0 + kTileM * i, it.hq, it.b);
+        }
+        return true;
+      };
+      auto load_kv = [&](const CUtensorMap* tm, int j) -> bool {
+        const uint32_t slot = kv_prod % NS;
+        if (!mbar_wait(&s.kv_empty[slot], ((kv_prod / NS) & 1) ^ 1, ctx, kRoleTma)) return false;
+        ++kv_prod;
+        mbar_arrive_expect_tx(&s.kv_full[slot], kTileBytes);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_4d(s.kv[slot] + h * kHalfBytes, tm, &s.kv_full[slot], h * 64, j * kTileN, it.hkv, it.b);
+        }
+        return true;
+      };
+
+      if (it.n[0] > 0 && !load_q(0)) return;
+      if (!load_kv(&p.tm_k, 0)) return;
+      if (it.n[1] > 0 && !load_q(1)) return;
+      for (int j = 0; j < nmax; ++j) {
+        if (!load_kv(&p.tm_v, j)) return;
+        if (j + 1 < nmax && !load_kv(&p.tm_k, j + 1)) return;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// kernel
+// ------------------------------------------------------------------------------------
+template <typename T, int D, int NS>
+__global__ void __launch_bounds__(kFaThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  using Smem = FaSmem<D, NS>;
+  Smem& s = *reinterpret_cast<Smem*>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  AbortCtx ctx{&s.abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.q_full[i], 1);
+      mbar_init(&s.q_empty[i], 1);
+      mbar_init(&s.s_full[i], 1);
+      mbar_init(&s.p_full[i], 8);
+      mbar_init(&s.corr_full[i], 4);
+      mbar_init(&s.corr_empty[i], 4);
+      mbar_init(&s.o_full[i], 1);
+    }
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&s.kv_full[i], 1);
+      mbar_init(&s.kv_empty[i], 1);
+    }
+    mbar_init(&s.drain, 1);
+    fence_mbar_init();
+    if ((smem_u32(smem_raw) & 1023u) != 0u) raise_abort(ctx, kStatusSmemMisaligned);
+  }
+  if (warp == 13 && lane == 0) {
+    prefetch_tensormap(&p.tm_q);
+    prefetch_tensormap(&p.tm_k);
+    prefetch_tensormap(&p.tm_v);
+  }
+  if (warp == 12) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  const bool run = (s.abort_flag == 0);
+
+  if (warp < 8) {
+    reg_inc<192>();
+    if (run) fa_softmax_role<T, D, NS>(p, s, ctx, tmem, warp >> 2);
+  } else if (warp < 12) {
+    reg_dec<80>();
+    if (run) fa_correction_role<T, D, NS>(p, s, ctx, tmem);
+  } else {
+    reg_dec<48>();
+    if (run && lane == 0) {
+      if (warp == 12) {
+        fa_mma_role<T, D, NS>(p, s, ctx, tmem);
+        if (s.abort_flag) {
+          // aborting: let the tensor pipe drain before TMEM is released
+          umma_commit(&s.drain);
+          mbar_wait(&s.drain, 0, ctx, kRoleDrain);
+        }
+      } else if (warp == 13) {
+        fa_tma_role<T, D, NS>(p, s, ctx);
+      }
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace hb

@@ -1,0 +1,201 @@
+/*
+ * heddle_b200 — C ABI of the B200-native attention / fused-GEMM hot path.
+ *
+ * The reference (DragonOV12341/Heddle) has no C boundary of its own: its device
+ * kernels are generated at run time by TileLang and reached through Python
+ * callables.  Each entry point below names the reference callable it replaces
+ * (path inside the reference project : line).
+ *
+ * Conventions
+ *   - every pointer named q/k/v/o/lse/a/w/out/... is a DEVICE pointer owned by the
+ *     caller; the library never allocates or frees caller memory;
+ *   - all calls are stream-ordered and asynchronous: they enqueue work on `stream`
+ *     (a cudaStream_t passed as void*, NULL = legacy default stream) and return;
+ *   - the return value is an hb_status; on failure hb_last_error() returns a
+ *     thread-local, human readable message.  No exception, abort() or device trap
+ *     ever crosses this boundary;
+ *   - strides are in ELEMENTS of the tensor's dtype, the innermost (head_dim /
+ *     K / N) dimension is contiguous.
+ */
+#ifndef HEDDLE_B200_H_
+#define HEDDLE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HB_VERSION 100
+
+typedef enum hb_status {
+  HB_OK = 0,
+  HB_ERR_BAD_ARG = 1,     /* null pointer, negative size, inconsistent shape      */
+  HB_ERR_UNSUPPORTED = 2, /* dtype / head_dim / epilogue not built for sm_100a     */
+  HB_ERR_ALIGN = 3,       /* pointer or stride violates the 16-byte TMA rule       */
+  HB_ERR_CUDA = 4,        /* a CUDA runtime / driver call failed                   */
+  HB_ERR_TIMEOUT = 5      /* a device-side bounded wait gave up (see hb_status_word) */
+} hb_status;
+
+typedef enum hb_dtype {
+  HB_BF16 = 0,
+  HB_FP16 = 1,
+  HB_FP8_E4M3 = 2
+} hb_dtype;
+
+/* hb_query() selectors */
+enum {
+  HB_QUERY_SM_COUNT = 0,
+  HB_QUERY_SMEM_OPTIN = 1,
+  HB_QUERY_CC = 2, /* major*10+minor of the current device */
+  HB_QUERY_FA_SMEM = 3,
+  HB_QUERY_GEMM_SMEM = 4
+};
+
+/*
+ * FlashAttention forward:  O = softmax(Q K^T * softmax_scale + mask) V,
+ * optionally LSE = log(sum(exp(scaled masked scores))) per query row (natural log).
+ *
+ * Replaces the kernels produced by
+ *   Heddle/heddle/tileop/flash_attention.py:20-143   (flashattn)
+ *   Heddle/heddle/tileop/flash_attention.py:158-300  (flashattn_lse)
+ *   Heddle/heddle/frontend/backend.py:28-85, 92-156  (_build_fa_kernel[_with_lse])
+ * and is what _tilelang_sdpa_direct (backend.py:205-224) and
+ * TileLangFlashAttnFunc.forward (patterns.py:146-187) launch.
+ *
+ * Layout: q is [B, Hq, Sq, D], k/v are [B, Hkv, Skv, D], o is [B, Hq, Sq, D], each
+ * addressed through explicit batch/head/seq strides so that both BHSD and BSHD
+ * storage work without a transposed copy.  Query head h reads KV head
+ * h / (Hq / Hkv).  Causal masking follows the reference's past_len rule
+ * (flash_attention.py:27,44): query i may see key j iff j <= i + (Skv - Sq).
+ *
+ * FP8: q/k/v are e4m3 with per-tensor dequantisation scales q_scale/k_scale/v_scale;
+ * P is requantised to e4m3 (scale p_scale, 0 = library default) before the PV MMA;
+ * o is bf16.
+ */
+typedef struct hb_fa_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse; /* optional [B, Hq, Sq] fp32 contiguous; NULL = not written */
+  int32_t B, Hq, Hkv, Sq, Skv, D;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  int64_t k_stride_b, k_stride_h, k_stride_s;
+  int64_t v_stride_b, v_stride_h, v_stride_s;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  int32_t causal;
+  float softmax_scale; /* <= 0 selects D^-1/2 */
+  int32_t dtype;       /* hb_dtype of q/k/v (o: same dtype; bf16 for FP8) */
+  float q_scale, k_scale, v_scale, p_scale, o_scale; /* FP8 only; 0 = 1.0 */
+  void* stream;
+} hb_fa_args;
+
+int hb_fa_fwd(const hb_fa_args* args);
+
+/*
+ * H2O score:  score[b,h,k] = sum_q exp(scaled masked score[q,k] - LSE[q])
+ * Replaces Heddle/heddle/tileop/h2o_attention.py:27-136 (h2o_score), called from
+ * backend.py:162-202 (_tilelang_h2o_attention).  lse is the natural-log LSE that
+ * hb_fa_fwd writes; score is [B, Hq, Skv] fp32 and is overwritten.
+ */
+typedef struct hb_h2o_args {
+  const void* q;
+  const void* k;
+  const float* lse;
+  float* score;
+  int32_t B, Hq, Hkv, Sq, Skv, D;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  int64_t k_stride_b, k_stride_h, k_stride_s;
+  int32_t causal;
+  float softmax_scale;
+  int32_t dtype;
+  void* stream;
+} hb_h2o_args;
+
+int hb_h2o_score(const hb_h2o_args* args);
+
+/*
+ * GEMM + fused epilogue:  out[M, N_out] = epilogue(a[M, K] . w[N, K]^T)
+ *
+ * Replaces the kernels emitted by
+ *   Heddle/heddle/frontend/codegen.py:980-1244 (auto_gemm_* : GEMM + unary epilogue,
+ *     dual-GEMM / SwiGLU with the activation left in PyTorch at :1155-1160)
+ *   Heddle/heddle/frontend/backend.py:227-252  (_build_gemm_kernel)
+ * `w` is in nn.Linear layout [N, K] (K contiguous) — no transposed weight copy is
+ * needed (the reference caches one, codegen.py:1124-1131).
+ *
+ * Epilogues (fp32 on the accumulator, then cast; formulas codegen.py:1232-1244):
+ *   NONE, SILU, RELU, GELU_TANH, SIGMOID, TANH           out is [M, N]
+ *   SWIGLU      w = [Wg ; Wu] stacked as [2*N_out, K];    out[M, N_out] = silu(g) * u
+ *   ROWSCALE    out = row_scale[m] * acc   (RMSNorm with gamma folded into w)
+ *   ROPE        rotate-half RoPE on head_dim-wide column groups,
+ *               cos/sin tables [rope_seq, head_dim/2] fp32, position = m % rope_seq
+ * Optional operands: row_scale (fp32 [M]) may accompany any epilogue and is applied
+ * first; residual ([M, N_out], out dtype) is added last.
+ */
+typedef enum hb_epilogue {
+  HB_EPI_NONE = 0,
+  HB_EPI_SILU = 1,
+  HB_EPI_RELU = 2,
+  HB_EPI_GELU_TANH = 3,
+  HB_EPI_SIGMOID = 4,
+  HB_EPI_TANH = 5,
+  HB_EPI_SWIGLU = 6,
+  HB_EPI_ROPE = 7
+} hb_epilogue;
+
+typedef struct hb_gemm_args {
+  const void* a; /* [M, K], row stride lda */
+  const void* w; /* [N, K], row stride ldw */
+  void* out;     /* [M, N_out], row stride ldo */
+  int32_t M, N, K;
+  int64_t lda, ldw, ldo;
+  int32_t dtype; /* HB_BF16 or HB_FP16 */
+  int32_t epilogue;
+  const float* row_scale;  /* optional fp32 [M] */
+  const void* residual;    /* optional [M, N_out], row stride ldr */
+  int64_t ldr;
+  const float* rope_cos;   /* ROPE: [rope_seq, head_dim/2] */
+  const float* rope_sin;
+  int32_t rope_seq, head_dim;
+  int32_t rope_cols;       /* ROPE: columns [0, rope_cols) are rotated, the rest copied */
+  void* stream;
+} hb_gemm_args;
+
+int hb_gemm_epilogue(const hb_gemm_args* args);
+
+/*
+ * Row statistic for RMSNorm fused with the residual add:
+ *   y = x (+ residual);  if y_out: y_out = y;  rstd[m] = rsqrt(mean(y^2) + eps)
+ * The reference only analyses this fusion (Heddle/heddle/frontend/elementwise_fusion.py:73-80)
+ * and runs RMSNorm in eager PyTorch; here it feeds the ROWSCALE GEMM epilogue.
+ */
+int hb_rms_rowstat(const void* x, const void* residual, void* y_out, float* rstd,
+                   int32_t M, int32_t N, int64_t ldx, float eps, int32_t dtype, void* stream);
+
+/* Device-side status word of the current device (0 = no bounded wait ever gave up);
+ * reading it synchronises the device. */
+int hb_status_word(uint32_t* out);
+
+/* Library / device information. */
+int hb_version(void);
+int hb_query(int what);
+const char* hb_last_error(void);
+/* Releases the per-device caches (status word, driver entry points). */
+int hb_shutdown(void);
+
+/*
+ * Diagnostics: one tcgen05 MMA tile through the library's own descriptor helpers.
+ *   mode 0: out[128,128] fp32 = A[128,K] . B[128,K]^T          (both K-major in smem)
+ *   mode 1: out[128,N]  fp32 = P[128,128] . V[128,N]           (P from TMEM, V MN-major)
+ * a, b are dense row-major device arrays of `dtype`; K, N in {64, 128}.
+ * No reference counterpart; used by the test-suite to pin the operand layouts.
+ */
+int hb_debug_umma(int mode, const void* a, const void* b, float* out, int32_t kn, int32_t dtype,
+                  void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HEDDLE_B200_H_ */
