@@ -1,0 +1,3 @@
+"""Kernel factories with the reference's calling protocol (Heddle/heddle/tileop/)."""
+from .flash_attention import flashattn, flashattn_lse  # noqa: F401
+from .h2o_attention import h2o_score  # noqa: F401

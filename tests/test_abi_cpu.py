@@ -1,0 +1,102 @@
+"""The C-ABI library builds for sm_100a, loads on a machine without a GPU and exports
+every symbol include/heddle_b200.h declares.  No compute call is made here."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "heddle_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(built_lib):
+    from heddle_b200 import _lib
+    declared = _declared_symbols()
+    assert declared, "no declarations found in the header"
+    assert sorted(_lib.EXPORTS) == declared
+    for name in declared:
+        assert hasattr(built_lib, name), name
+
+
+def test_version_and_static_queries(built_lib):
+    from heddle_b200 import _lib
+    assert built_lib.hb_version() == 100
+    fa_smem = built_lib.hb_query(_lib.HB_QUERY_FA_SMEM)
+    assert 0 < fa_smem <= 227 * 1024
+
+
+def test_struct_layout_matches_header(built_lib):
+    """ctypes mirrors of the argument structs have the C compiler's layout."""
+    import subprocess, sys, tempfile
+    from heddle_b200 import _lib
+    src = r'''
+#include <stdio.h>
+#include <stddef.h>
+#include "heddle_b200.h"
+int main(void) {
+  printf("%zu %zu %zu %zu\n", sizeof(hb_fa_args), offsetof(hb_fa_args, causal), offsetof(hb_fa_args, stream),
+         offsetof(hb_fa_args, q_stride_b));
+  printf("%zu %zu %zu\n", sizeof(hb_gemm_args), offsetof(hb_gemm_args, row_scale), offsetof(hb_gemm_args, stream));
+  printf("%zu %zu\n", sizeof(hb_h2o_args), offsetof(hb_h2o_args, stream));
+  return 0;
+}'''
+    with tempfile.TemporaryDirectory() as d:
+        c = Path(d) / "t.c"
+        c.write_text(src)
+        exe = Path(d) / "t"
+        subprocess.run(["gcc", "-std=c99", "-I", str(ROOT / "include"), str(c), "-o", str(exe)], check=True)
+        lines = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split("\n")
+    fa = [int(x) for x in lines[0].split()]
+    assert fa == [ctypes.sizeof(_lib.FaArgs), _lib.FaArgs.causal.offset, _lib.FaArgs.stream.offset,
+                  _lib.FaArgs.q_stride_b.offset]
+    gm = [int(x) for x in lines[1].split()]
+    assert gm == [ctypes.sizeof(_lib.GemmArgs), _lib.GemmArgs.row_scale.offset, _lib.GemmArgs.stream.offset]
+    h2 = [int(x) for x in lines[2].split()]
+    assert h2 == [ctypes.sizeof(_lib.H2oArgs), _lib.H2oArgs.stream.offset]
+
+
+def test_argument_validation_needs_no_gpu(built_lib):
+    """Checks that run before any CUDA call return error codes with a message."""
+    from heddle_b200 import _lib
+    assert built_lib.hb_fa_fwd(None) == _lib.HB_ERR_BAD_ARG
+    assert b"NULL" in built_lib.hb_last_error()
+    a = _lib.FaArgs()
+    a.B, a.Hq, a.Hkv, a.Sq, a.Skv, a.D = 1, 6, 4, 128, 128, 128
+    assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_ERR_BAD_ARG  # Hq % Hkv
+    a.Hq = 4
+    a.D = 96
+    assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_ERR_UNSUPPORTED
+    assert b"head_dim" in built_lib.hb_last_error()
+    a.D = 128
+    a.Skv = 64
+    a.causal = 1
+    assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_ERR_UNSUPPORTED  # causal with Skv < Sq
+    a.causal = 0
+    a.Skv = 0
+    assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_ERR_BAD_ARG
+    a.Skv = 128
+    assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_ERR_BAD_ARG  # null pointers
+    a.Sq = 0
+    assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_OK  # empty problem is a no-op
+
+
+def test_ops_reject_cpu_tensors(built_lib):
+    from heddle_b200 import ops
+    q = torch.zeros(1, 1, 128, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ops.fa_fwd(q, q, q)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from heddle_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setenv("HEDDLE_B200_LIB", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="not found"):
+        _lib.load()
