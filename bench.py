@@ -1,0 +1,334 @@
+#!/usr/bin/env python
+"""Benchmark of the attention-forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one FlashAttention-forward pass over one synthetic batch of the headline
+workload: BF16 causal multi-head attention, B=4, H=32, S=4096, D=128 (per GPU).  With
+N > 1 (launched under torchrun, one rank per GPU) every rank runs the same-sized shard
+of a global batch of 4*N — attention shards by batch x head with no collective — so the
+scaling is weak and ``value`` is the whole-job TFLOP/s: total algorithmic FLOPs over
+the slowest rank's time.
+
+Printed by rank 0 as ONE JSON line:
+  value      device-resident throughput (inputs already in HBM), CUDA events, max over ranks
+  e2e        same metric through the public op with HOST buffers: pinned H2D of q,k,v and
+             D2H of O and LSE inside the timed region, every step
+  roofline   dominant kernel (fa_fwd) against the measured dense-bf16 tensor peak
+  cpu_baseline  the CPU oracle (the reference's eager fp32 graph) on a bounded slice
+  clocks     SM clock / throttle reasons sampled during the timed region
+
+``--impl reference`` times the reference's own CPU path for the same metric/config:
+its FX graph executed eagerly in fp32 by PyTorch on the host cores (the oracle port).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+WORKLOAD = dict(B=4, H=32, S=4096, D=128, causal=True)
+METRIC = "attention_fwd_bf16_causal_tflops"
+UNIT = "TFLOP/s"
+
+
+def algorithmic_flops(B, H, S, D, causal) -> float:
+    # 4*B*H*Sq*Skv*D for both GEMMs; causal with Sq == Skv counts half (masked tiles are not work)
+    return 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(burst=float(d["bf16_tflops"]), sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    hbm=float(d["hbm_gbs"]), source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------------------
+# clock sampling during the timed region (read-only NVML queries)
+# ----------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x0000000000000004: "sw_power_cap",
+        0x0000000000000008: "hw_slowdown",
+        0x0000000000000020: "sw_thermal_slowdown",
+        0x0000000000000040: "hw_thermal_slowdown",
+        0x0000000000000080: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, device_index: int, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        self.period = period_s
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            # honour CUDA_VISIBLE_DEVICES: map through the PCI bus id of the torch device
+            bus = torch.cuda.get_device_properties(device_index).pci_bus_id if hasattr(
+                torch.cuda.get_device_properties(device_index), "pci_bus_id") else None
+            self._h = None
+            if bus is not None:
+                for i in range(pynvml.nvmlDeviceGetCount()):
+                    h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                    info = pynvml.nvmlDeviceGetPciInfo(h)
+                    if int(info.bus) == int(bus):
+                        self._h = h
+                        break
+            if self._h is None:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------
+# CPU legs (the oracle is only ever the thing compared against or timed as the baseline)
+# ----------------------------------------------------------------------------------------
+def cpu_slice_tflops(heads: int = 2, reps: int = 3):
+    """Reference eager fp32 attention on the host cores for a slice of the workload:
+    one batch element x ``heads`` query heads at full sequence length."""
+    from oracle import attention_oracle as O
+
+    S, D = WORKLOAD["S"], WORKLOAD["D"]
+    q, k, v = O.make_qkv(1, heads, heads, S, S, D, seed=0, dtype=torch.bfloat16)
+    O.attention_eager(q, k, v, causal=True)  # warm-up
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        O.attention_eager(q, k, v, causal=True)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    fl = algorithmic_flops(1, heads, S, D, True)
+    return fl / t / 1e12, t, f"B=1 x {heads} heads x S={S} D={D} causal, eager fp32, median of {reps}"
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU implementation of the path (its FX graph run
+    eagerly in fp32 = the oracle port), all host threads, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    heads = 2
+    from oracle import attention_oracle as O
+    S, D = WORKLOAD["S"], WORKLOAD["D"]
+    q, k, v = O.make_qkv(1, heads, heads, S, S, D, seed=0, dtype=torch.bfloat16)
+    steps = max(1, min(args.steps, 20))
+    warm = max(1, min(args.warmup, 2))
+    for _ in range(warm):
+        O.attention_eager(q, k, v, causal=True)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.attention_eager(q, k, v, causal=True)
+    dt = (time.perf_counter() - t0) / steps
+    val = algorithmic_flops(1, heads, S, D, True) / dt / 1e12
+    sample = f"each step = B=1 x {heads} heads x S={S} D={D} causal slice of the workload (1/{4 * 32 // heads} of it)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "bf16_causal_mha_B4_H32_S4096_D128", "global_batch": WORKLOAD["B"] * args.gpus,
+                   "seq_len": S, "heads": WORKLOAD["H"], "head_dim": D, "causal": True, "parallelism": "cpu"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------------
+def run_ours(args):
+    from heddle_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    distributed = world > 1
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if distributed:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if not distributed:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    B, H, S, D, causal = (WORKLOAD[k] for k in ("B", "H", "S", "D", "causal"))
+    flops_rank = algorithmic_flops(B, H, S, D, causal)
+    # this rank's shard of the global batch: same generator stream, distinct seed per rank
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q = torch.randn(B, H, S, D, generator=gen, device=dev).to(torch.bfloat16)
+    k = torch.randn(B, H, S, D, generator=gen, device=dev).to(torch.bfloat16)
+    v = torch.randn(B, H, S, D, generator=gen, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+
+    # ---- device-resident throughput -----------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        ops.fa_fwd(q, k, v, causal=causal, out=out)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            ops.fa_fwd(q, k, v, causal=causal, out=out)
+        stop.record()
+        barrier()
+    ms_total = max_over_ranks(start.elapsed_time(stop))
+    ms_step = ms_total / args.steps
+    value = flops_rank * world / (ms_step * 1e-3) / 1e12
+    status = ops.status_word()
+
+    # ---- per-launch duration of the dominant kernel (for the roofline) ---------------------
+    n_ev = min(args.steps, 50)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_ev)]
+    for a, b in evs:
+        a.record()
+        ops.fa_fwd(q, k, v, causal=causal, out=out)
+        b.record()
+    torch.cuda.synchronize()
+    launch_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    peaks = load_peaks()
+    sustained_run = ms_total > 1000.0
+    peak = peaks["sustained"] if sustained_run else peaks["burst"]
+    achieved = flops_rank / (launch_ms * 1e-3) / 1e12
+    traffic = None
+    tfile = ROOT / "profiles" / "fa_fwd_dram_traffic.json"
+    if tfile.exists():
+        try:
+            traffic = json.loads(tfile.read_text()).get("bytes_per_launch_full_workload")
+        except Exception:
+            traffic = None
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": traffic, "kernel": "fa_fwd_kernel<bf16,128>",
+                "peak_kind": f"{'sustained' if sustained_run else 'burst'} dense bf16, of {peaks['source']}",
+                "frac_of_burst_peak": achieved / peaks["burst"], "launch_ms": launch_ms}
+
+    # ---- end to end through the public op with host buffers --------------------------------
+    hq, hk, hv = (torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in (q, k, v))
+    ho = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
+    hl = torch.empty((B, H, S), dtype=torch.float32, pin_memory=True)
+
+    def e2e_step():
+        dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
+        o, lse = ops.fa_fwd(dq, dk, dv, causal=causal, return_lse=True)
+        ho.copy_(o, non_blocking=True)
+        hl.copy_(lse, non_blocking=True)
+
+    e2e = None
+    if not args.kernel_only:
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        start.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        stop.record()
+        barrier()
+        e2e_ms = max_over_ranks(start.elapsed_time(stop)) / e2e_steps
+        h2d = 3 * q.numel() * q.element_size()
+        d2h = ho.numel() * ho.element_size() + hl.numel() * 4
+        e2e = {"value": flops_rank * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms}
+
+    # ---- CPU baseline (rank 0, N = 1 only) -------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.kernel_only:
+        v_cpu, t_cpu, sample = cpu_slice_tflops()
+        cpu = {"value": v_cpu, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+               "sample": sample + f" ({t_cpu:.3f} s per slice)"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "bf16_causal_mha_B4_H32_S4096_D128", "global_batch": B * world, "seq_len": S,
+                       "heads": H, "head_dim": D, "causal": True, "parallelism": f"dp{world}_batch_x_head_no_collective",
+                       "l2": "inputs+outputs (268 MB per step) exceed the 126 MB L2; no explicit flush"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * world,
+            "clocks": clocks.summary(), "device_status_word": status,
+            "pct_of_nominal_dense_bf16_peak_2250": 100.0 * value / world / 2250.0,
+        }
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the heddle_b200 kernels have no CPU path")
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -68,7 +68,7 @@ class GemmArgs(C.Structure):
         ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
         ("lda", C.c_int64), ("ldw", C.c_int64), ("ldo", C.c_int64),
         ("dtype", C.c_int32), ("epilogue", C.c_int32),
-        ("row_scale", C.c_void_p), ("residual", C.c_void_p), ("ldr", C.c_int64),
+        ("row_scale", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p), ("ldr", C.c_int64),
         ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
         ("rope_seq", C.c_int32), ("head_dim", C.c_int32), ("rope_cols", C.c_int32),
         ("stream", C.c_void_p),

@@ -284,6 +284,7 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
+          __syncwarp();  // reconverge after the predicated stores of the previous chunk
           tmem_ld32(tO + c * 32, r);
           tmem_wait_ld();
           if (live) {

@@ -1,12 +1,168 @@
-// placeholder translation unit: replaced by the tcgen05 GEMM + epilogue kernels
+// hb_gemm_epilogue / hb_rms_rowstat: validation, TMA descriptors and launch.
+#include "gemm_sm100.cuh"
 #include "host_common.h"
+
+#include <algorithm>
+
 namespace hb {
-int gemm_smem_bytes() { return 0; }
+
+template <typename T, int EPI>
+static int launch_gemm(const GemmParams& p, int grid, const DeviceState* st, cudaStream_t stream) {
+  if ((int)sizeof(GemmSmem) > st->smem_optin)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: kernel needs %d bytes of shared memory, device offers %d",
+                     (int)sizeof(GemmSmem), st->smem_optin);
+  auto kernel = gemm_kernel<T, EPI>;
+  static bool configured[64] = {};
+  if (!configured[st->device & 63]) {
+    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GemmSmem)));
+    configured[st->device & 63] = true;
+  }
+  kernel<<<grid, kGemmThreads, sizeof(GemmSmem), stream>>>(p);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB_OK;
 }
+
+template <typename T>
+static int dispatch_gemm(int epi_class, const GemmParams& p, int grid, const DeviceState* st, cudaStream_t stream) {
+  switch (epi_class) {
+    case kEpiPlain:
+      return launch_gemm<T, kEpiPlain>(p, grid, st, stream);
+    case kEpiSwiglu:
+      return launch_gemm<T, kEpiSwiglu>(p, grid, st, stream);
+    default:
+      return launch_gemm<T, kEpiRope>(p, grid, st, stream);
+  }
+}
+
+static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+static int gemm_impl(const hb_gemm_args* a) {
+  if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: args is NULL");
+  if (a->M < 0 || a->N <= 0 || a->K <= 0)
+    return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: bad extents M=%d N=%d K=%d", a->M, a->N, a->K);
+  if (a->dtype != HB_BF16 && a->dtype != HB_FP16)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: dtype %d not supported (bf16, fp16)", a->dtype);
+  if (a->epilogue < HB_EPI_NONE || a->epilogue > HB_EPI_ROPE)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: unknown epilogue %d", a->epilogue);
+  int n_out = a->N;
+  int epi_class = kEpiPlain;
+  if (a->epilogue == HB_EPI_SWIGLU) {
+    if (a->N % 2 != 0) return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: SWIGLU needs an even N (stacked [Wg; Wu])");
+    n_out = a->N / 2;
+    epi_class = kEpiSwiglu;
+  } else if (a->epilogue == HB_EPI_ROPE) {
+    epi_class = kEpiRope;
+    if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256)
+      return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: ROPE head_dim %d not supported (64, 128, 256)", a->head_dim);
+    if (a->N % a->head_dim != 0 || a->rope_cols % a->head_dim != 0 || a->rope_cols < 0 || a->rope_cols > a->N)
+      return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: ROPE needs head_dim | N and head_dim | rope_cols <= N");
+    if (a->rope_cos == nullptr || a->rope_sin == nullptr || a->rope_seq <= 0)
+      return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: ROPE needs cos/sin tables and rope_seq > 0");
+  }
+  if (a->M == 0) return HB_OK;
+  if (a->a == nullptr || a->w == nullptr || a->out == nullptr)
+    return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: a, w and out must be non-NULL");
+  if ((a->K % 8) || (n_out % 8) || (a->lda % 8) || (a->ldw % 8) || (a->ldo % 8) ||
+      (a->residual != nullptr && (a->ldr % 8)))
+    return set_error(HB_ERR_ALIGN, "hb_gemm_epilogue: K, N_out and the leading dimensions must be multiples of 8");
+  if (a->lda < a->K || a->ldw < a->K || a->ldo < n_out || (a->residual != nullptr && a->ldr < n_out))
+    return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: a leading dimension is smaller than its row");
+  if (!aligned16(a->a) || !aligned16(a->w) || !aligned16(a->out) || !aligned16(a->residual) || !aligned16(a->bias))
+    return set_error(HB_ERR_ALIGN, "hb_gemm_epilogue: pointers must be 16-byte aligned");
+
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != HB_OK) return rc;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const CUtensorMapDataType dt = a->dtype == HB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const uint32_t box[2] = {(uint32_t)kGemmBK, 128};
+  {
+    const uint64_t dims[2] = {(uint64_t)a->K, (uint64_t)a->M};
+    const uint64_t str[1] = {(uint64_t)a->lda * 2};
+    rc = encode_tensor_map(&p.tm_a, dt, 2, a->a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)a->K, (uint64_t)a->N};
+    const uint64_t str[1] = {(uint64_t)a->ldw * 2};
+    rc = encode_tensor_map(&p.tm_w, dt, 2, a->w, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  }
+  p.out = a->out;
+  p.row_scale = a->row_scale;
+  p.residual = a->residual;
+  p.bias = a->bias;
+  p.rope_cos = a->rope_cos;
+  p.rope_sin = a->rope_sin;
+  p.status = st->status_word;
+  p.ldo = a->ldo;
+  p.ldr = a->ldr;
+  p.M = a->M;
+  p.N_out = n_out;
+  p.K = a->K;
+  p.tile_cols = epi_class == kEpiSwiglu ? 128 : kGemmBN;
+  p.tiles_m = (a->M + kGemmBM - 1) / kGemmBM;
+  p.tiles_n = (n_out + p.tile_cols - 1) / p.tile_cols;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n;
+  if (tiles > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: too many tiles");
+  p.num_tiles = (int)tiles;
+  p.k_steps = (a->K + kGemmBK - 1) / kGemmBK;
+  p.act = (a->epilogue >= HB_EPI_SILU && a->epilogue <= HB_EPI_TANH) ? a->epilogue : kActNone;
+  p.rope_seq = a->rope_seq;
+  p.head_dim = a->head_dim;
+  p.rope_cols = a->rope_cols;
+  p.w_row2_offset = n_out;
+
+  const int grid = (int)std::min<long long>(tiles, st->sm_count);
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  return a->dtype == HB_BF16 ? dispatch_gemm<__nv_bfloat16>(epi_class, p, grid, st, stream)
+                             : dispatch_gemm<__half>(epi_class, p, grid, st, stream);
+}
+
+static int rowstat_impl(const void* x, const void* residual, void* y_out, float* rstd, int M, int N, long long ldx,
+                        float eps, int dtype, void* stream) {
+  if (M < 0 || N <= 0) return set_error(HB_ERR_BAD_ARG, "hb_rms_rowstat: bad extents M=%d N=%d", M, N);
+  if (dtype != HB_BF16 && dtype != HB_FP16) return set_error(HB_ERR_UNSUPPORTED, "hb_rms_rowstat: dtype %d", dtype);
+  if (M == 0) return HB_OK;
+  if (x == nullptr || rstd == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_rms_rowstat: x and rstd must be non-NULL");
+  if ((N % 8) || (ldx % 8) || ldx < N || !aligned16(x) || !aligned16(residual) || !aligned16(y_out))
+    return set_error(HB_ERR_ALIGN, "hb_rms_rowstat: N and ldx must be multiples of 8, pointers 16-byte aligned");
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != HB_OK) return rc;
+  const int grid = (M + 7) / 8;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == HB_BF16) {
+    rms_rowstat_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+        static_cast<__nv_bfloat16*>(y_out), rstd, M, N, ldx, eps);
+  } else {
+    rms_rowstat_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<const __half*>(residual),
+                                                    static_cast<__half*>(y_out), rstd, M, N, ldx, eps);
+  }
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB_OK;
+}
+
+int gemm_smem_bytes() { return (int)sizeof(GemmSmem); }
+
+}  // namespace hb
+
 extern "C" {
-int hb_gemm_epilogue(const hb_gemm_args*) { return hb::set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: not built yet"); }
-int hb_rms_rowstat(const void*, const void*, void*, float*, int32_t, int32_t, int64_t, float, int32_t, void*) {
-  return hb::set_error(HB_ERR_UNSUPPORTED, "hb_rms_rowstat: not built yet");
+
+int hb_gemm_epilogue(const hb_gemm_args* args) {
+  hb::clear_error();
+  return hb::gemm_impl(args);
 }
+
+int hb_rms_rowstat(const void* x, const void* residual, void* y_out, float* rstd, int32_t M, int32_t N, int64_t ldx,
+                   float eps, int32_t dtype, void* stream) {
+  hb::clear_error();
+  return hb::rowstat_impl(x, residual, y_out, rstd, M, N, ldx, eps, dtype, stream);
+}
+
 int hb_h2o_score(const hb_h2o_args*) { return hb::set_error(HB_ERR_UNSUPPORTED, "hb_h2o_score: not built yet"); }
-}
+
+}  // extern "C"

@@ -1,0 +1,425 @@
+// tcgen05 GEMM with fused epilogues for sm_100a:  out[M, N_out] = epilogue(a[M,K] . w[N,K]^T)
+//
+// Both operands are K-major (activations row-major, weights in nn.Linear layout), so
+// TMA brings 128-byte-swizzled [rows x 64] slabs straight into the layout tcgen05.mma
+// consumes and no transposed weight copy exists (the reference makes one,
+// Heddle/heddle/frontend/codegen.py:1124-1131).  Epilogue arithmetic restates
+// codegen.py:1204-1244 (fp32 on the accumulator, then cast).
+//
+// Persistent, warp-specialised CTA (192 threads), one 128 x 256 accumulator tile at a time:
+//   warp 0     TMA producer: a 4-deep ring of {A 128x64, B 256x64} stages behind mbarriers
+//   warp 1     MMA issuer: one thread, tcgen05.mma M=128 N=256 K=16, fp32 accumulators in
+//              TMEM, two accumulator buffers (2 x 256 columns) so the epilogue of tile t
+//              overlaps the main loop of tile t+1
+//   warps 2-5  epilogue: TMEM -> registers -> epilogue math -> 16-byte global stores
+//
+// Epilogue classes:
+//   PLAIN   row_scale, bias, unary activation, residual              (256 output columns / tile)
+//   SWIGLU  B tile = 128 rows of Wg and the matching 128 rows of Wu;  out = silu(g) * u
+//           (128 output columns / tile; the reference leaves this product to PyTorch,
+//           codegen.py:1155-1160)
+//   ROPE    rotate-half rotary embedding on head_dim-wide column groups
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace hb {
+
+constexpr int kGemmThreads = 192;
+constexpr int kGemmBM = 128;
+constexpr int kGemmBN = 256;
+constexpr int kGemmBK = 64;
+constexpr int kGemmStages = 4;
+constexpr int kGemmGroupM = 16;  // M-tiles per rasterisation group (L2 reuse of the weight slabs)
+
+enum GemmEpiClass : int { kEpiPlain = 0, kEpiSwiglu = 1, kEpiRope = 2 };
+enum GemmAct : int { kActNone = 0, kActSilu = 1, kActRelu = 2, kActGeluTanh = 3, kActSigmoid = 4, kActTanh = 5 };
+enum GemmRole : uint32_t { kGemmRoleTma = 0x21, kGemmRoleMma = 0x22, kGemmRoleEpi = 0x23, kGemmRoleDrain = 0x24 };
+
+struct alignas(64) GemmParams {
+  CUtensorMap tm_a;
+  CUtensorMap tm_w;
+  void* out;
+  const float* row_scale;
+  const void* residual;
+  const void* bias;
+  const float* rope_cos;
+  const float* rope_sin;
+  uint32_t* status;
+  long long ldo, ldr;
+  int M, N_out, K;
+  int tile_cols;  // output columns per tile (256, or 128 for SWIGLU)
+  int tiles_m, tiles_n, num_tiles, k_steps;
+  int act;
+  int rope_seq, head_dim, rope_cols;
+  int w_row2_offset;  // SWIGLU: first row of Wu inside the stacked weight
+};
+
+struct GemmSmem {
+  alignas(1024) uint8_t a[kGemmStages][kGemmBM * kGemmBK * 2];
+  alignas(1024) uint8_t b[kGemmStages][kGemmBN * kGemmBK * 2];
+  uint64_t full[kGemmStages], empty[kGemmStages];
+  uint64_t acc_full[2], acc_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+__device__ __forceinline__ void gemm_tile_coords(const GemmParams& p, int t, int& m_t, int& n_t) {
+  const int per_group = kGemmGroupM * p.tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * kGemmGroupM;
+  const int gsz = min(p.tiles_m - first_m, kGemmGroupM);
+  const int r = t - g * per_group;
+  m_t = first_m + r % gsz;
+  n_t = r / gsz;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case kActSilu:
+      return v * (1.0f / (1.0f + __expf(-v)));
+    case kActRelu:
+      return fmaxf(v, 0.0f);
+    case kActGeluTanh:
+      return v * 0.5f * (1.0f + tanhf(0.7978845608f * (v + 0.044715f * v * v * v)));
+    case kActSigmoid:
+      return 1.0f / (1.0f + __expf(-v));
+    case kActTanh:
+      return tanhf(v);
+    default:
+      return v;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& w, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& w, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 w;
+  w.x = Pack2<T>::pack(f[0], f[1]);
+  w.y = Pack2<T>::pack(f[2], f[3]);
+  w.z = Pack2<T>::pack(f[4], f[5]);
+  w.w = Pack2<T>::pack(f[6], f[7]);
+  return w;
+}
+
+// Stores 8 consecutive output values of one row (16 bytes), adding the residual if any.
+template <typename T>
+__device__ __forceinline__ void store8(const GemmParams& p, int row, int col, float (&v)[8]) {
+  if (p.residual != nullptr) {
+    float r[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + (long long)row * p.ldr + col), r);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] += r[i];
+  }
+  *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + (long long)row * p.ldo + col) = pack8<T>(v);
+}
+
+template <typename T>
+__device__ __forceinline__ void load_bias8(const GemmParams& p, int col, float (&b)[8]) {
+  unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + col), b);
+}
+
+// Epilogue of one accumulator tile for the row owned by this thread.  `tacc` carries the
+// warp's TMEM lane offset and the accumulator buffer's first column.
+template <typename T, int EPI>
+__device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t tacc, int m0, int n0, int row_in_tile) {
+  const int row = m0 + row_in_tile;
+  const bool row_ok = row < p.M;
+  const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
+
+  if constexpr (EPI == kEpiPlain) {
+#pragma unroll 1
+    for (int c = 0; c < kGemmBN / 32; ++c) {
+      uint32_t r[32];
+      __syncwarp();  // reconverge after the predicated stores of the previous chunk
+      tmem_ld32(tacc + c * 32, r);
+      tmem_wait_ld();
+      const int col = n0 + c * 32;
+      if (!row_ok || col >= p.N_out) continue;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (col + g * 8 >= p.N_out) break;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g * 8 + e]) * rs;
+        if (p.bias != nullptr) {
+          float b[8];
+          load_bias8<T>(p, col + g * 8, b);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] += b[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = apply_act(v[e], p.act);
+        store8<T>(p, row, col + g * 8, v);
+      }
+    }
+  } else if constexpr (EPI == kEpiSwiglu) {
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t rg[32], ru[32];
+      __syncwarp();
+      tmem_ld32(tacc + c * 32, rg);
+      tmem_ld32(tacc + 128 + c * 32, ru);
+      tmem_wait_ld();
+      const int col = n0 + c * 32;
+      if (!row_ok || col >= p.N_out) continue;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (col + g * 8 >= p.N_out) break;
+        float v[8], u[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          v[e] = __uint_as_float(rg[g * 8 + e]) * rs;
+          u[e] = __uint_as_float(ru[g * 8 + e]) * rs;
+        }
+        if (p.bias != nullptr) {
+          float bg[8], bu[8];
+          load_bias8<T>(p, col + g * 8, bg);
+          load_bias8<T>(p, p.w_row2_offset + col + g * 8, bu);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            v[e] += bg[e];
+            u[e] += bu[e];
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = v[e] * (1.0f / (1.0f + __expf(-v[e]))) * u[e];
+        store8<T>(p, row, col + g * 8, v);
+      }
+    }
+  } else {  // kEpiRope
+    const int hd = p.head_dim, half = hd >> 1;
+    const int pos = row_ok ? (row % p.rope_seq) : 0;
+    const float* cosr = p.rope_cos + (long long)pos * half;
+    const float* sinr = p.rope_sin + (long long)pos * half;
+#pragma unroll 1
+    for (int h0 = 0; h0 < kGemmBN; h0 += hd) {
+#pragma unroll 1
+      for (int c = 0; c < half; c += 32) {
+        uint32_t r1[32], r2[32];
+        __syncwarp();
+        tmem_ld32(tacc + h0 + c, r1);
+        tmem_ld32(tacc + h0 + half + c, r2);
+        tmem_wait_ld();
+        const int col = n0 + h0 + c;
+        if (!row_ok || col >= p.N_out) continue;
+        const bool rotate = col < p.rope_cols;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float x1[8], x2[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            x1[e] = __uint_as_float(r1[g * 8 + e]) * rs;
+            x2[e] = __uint_as_float(r2[g * 8 + e]) * rs;
+          }
+          if (p.bias != nullptr) {
+            float b1[8], b2[8];
+            load_bias8<T>(p, col + g * 8, b1);
+            load_bias8<T>(p, col + half + g * 8, b2);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              x1[e] += b1[e];
+              x2[e] += b2[e];
+            }
+          }
+          if (rotate) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float cs = cosr[c + g * 8 + e], sn = sinr[c + g * 8 + e];
+              const float a = x1[e], b = x2[e];
+              x1[e] = a * cs - b * sn;
+              x2[e] = b * cs + a * sn;
+            }
+          }
+          store8<T>(p, row, col + g * 8, x1);
+          store8<T>(p, row, col + half + g * 8, x2);
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  GemmSmem& s = *reinterpret_cast<GemmSmem*>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  AbortCtx ctx{&s.abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    for (int i = 0; i < kGemmStages; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.acc_full[i], 1);
+      mbar_init(&s.acc_empty[i], 4);
+    }
+    mbar_init(&s.drain, 1);
+    fence_mbar_init();
+    if ((smem_u32(smem_raw) & 1023u) != 0u) raise_abort(ctx, kStatusSmemMisaligned);
+    prefetch_tensormap(&p.tm_a);
+    prefetch_tensormap(&p.tm_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  const bool run = (s.abort_flag == 0);
+
+  if (warp == 0) {
+    if (run && lane == 0) {
+      // ---------------- TMA producer ----------------
+      constexpr uint32_t kStageBytes = (kGemmBM + kGemmBN) * kGemmBK * 2;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        int m_t, n_t;
+        gemm_tile_coords(p, t, m_t, n_t);
+        const int m0 = m_t * kGemmBM;
+        const int n0 = n_t * p.tile_cols;
+        const int row_b0 = n0;
+        const int row_b1 = (EPI == kEpiSwiglu) ? (p.w_row2_offset + n0) : (n0 + 128);
+        for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
+          const uint32_t st = it % kGemmStages;
+          if (!mbar_wait(&s.empty[st], ((it / kGemmStages) & 1) ^ 1, ctx, kGemmRoleTma)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&s.full[st], kStageBytes);
+          tma_load_2d(s.a[st], &p.tm_a, &s.full[st], ks * kGemmBK, m0);
+          tma_load_2d(s.b[st], &p.tm_w, &s.full[st], ks * kGemmBK, row_b0);
+          tma_load_2d(s.b[st] + 128 * kGemmBK * 2, &p.tm_w, &s.full[st], ks * kGemmBK, row_b1);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (run && lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, kGemmBM, kGemmBN, 0, 0);
+      constexpr uint64_t kDesc = (uint64_t(16 >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++tile_i) {
+        const uint32_t acc = tile_i & 1;
+        if (!mbar_wait(&s.acc_empty[acc], ((tile_i >> 1) & 1) ^ 1, ctx, kGemmRoleMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + acc * kGemmBN;
+        for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
+          const uint32_t st = it % kGemmStages;
+          if (!mbar_wait(&s.full[st], (it / kGemmStages) & 1, ctx, kGemmRoleMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a16 = smem_u32(s.a[st]) >> 4, b16 = smem_u32(s.b[st]) >> 4;
+#pragma unroll
+          for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+            umma_ss_f16(d_tmem, kDesc | (a16 + kk * 2), kDesc | (b16 + kk * 2), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&s.empty[st]);
+        }
+        if (ok) umma_commit(&s.acc_full[acc]);
+      }
+      if (s.abort_flag) {
+        umma_commit(&s.drain);
+        mbar_wait(&s.drain, 0, ctx, kGemmRoleDrain);
+      }
+    }
+    __syncwarp();
+  } else if (run) {
+    // ---------------- epilogue warps ----------------
+    const int quarter = warp & 3;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    uint32_t tile_i = 0;
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++tile_i) {
+      int m_t, n_t;
+      gemm_tile_coords(p, t, m_t, n_t);
+      const uint32_t acc = tile_i & 1;
+      if (!mbar_wait_warp(&s.acc_full[acc], (tile_i >> 1) & 1, ctx, kGemmRoleEpi)) break;
+      tc_fence_after();
+      gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, m_t * kGemmBM, n_t * p.tile_cols,
+                                quarter * 32 + lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm row statistic fused with the residual add (HBM-bound): one warp per row.
+//   y = x (+ residual), rounded to T;  rstd[m] = rsqrt(mean(y^2) + eps)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) rms_rowstat_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+                                                          T* __restrict__ y_out, float* __restrict__ rstd, int M,
+                                                          int N, long long ldx, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= M) return;
+  const T* xr = x + (long long)row * ldx;
+  const T* rr = residual != nullptr ? residual + (long long)row * ldx : nullptr;
+  T* yr = y_out != nullptr ? y_out + (long long)row * ldx : nullptr;
+  float acc = 0.f;
+  for (int c = lane * 8; c < N; c += 32 * 8) {
+    float v[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(xr + c), v);
+    if (rr != nullptr) {
+      float r[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(rr + c), r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += r[e];
+    }
+    const uint4 packed = pack8<T>(v);
+    if (yr != nullptr) *reinterpret_cast<uint4*>(yr + c) = packed;
+    float w[8];
+    unpack8<T>(packed, w);  // statistics of the rounded values, as a consumer of y sees them
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc += w[e] * w[e];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) rstd[row] = rsqrtf(acc / (float)N + eps);
+}
+
+}  // namespace hb

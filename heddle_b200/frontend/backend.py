@@ -1,0 +1,395 @@
+"""``torch.compile`` backend — counterpart of Heddle/heddle/frontend/backend.py.
+
+Surface kept from the reference: ``tilelang_backend(gm, example_inputs)`` (:1421), the
+``@torch.fx.wrap`` leaves ``_tilelang_sdpa_direct`` (:205) and ``_tilelang_h2o_attention``
+(:162) that the rewrites insert as single ``call_function`` nodes, the rewrite passes
+``_replace_sdpa_op`` (:906), ``_replace_expanded_attention`` (:688) and
+``try_fuse_h2o_attention`` (:1316), and the ``TILELANG_FRONTEND_*`` switches that gate
+them.  Underneath, the leaves call the sm_100a kernels through the C ABI; nothing is
+JIT-compiled and nothing falls back to eager attention.
+
+Deliberate differences from the reference (it follows the captured graph's meaning where
+the reference drops it):
+  * SDPA ``is_causal`` / ``scale`` and the scale constant of an expanded attention are
+    carried into the kernel call; the reference ignores them and instead assumes causal
+    whenever Sq == Skv (backend.py:215, :923-934);
+  * an additive mask is accepted only when it is provably the causal mask
+    (``triu(full(-inf), diagonal=Skv-Sq+1)``); any other mask, or dropout, leaves the
+    graph untouched instead of being silently discarded (backend.py:752-756);
+  * after attention is fused the GEMM + epilogue fusion pass still runs (the reference
+    stops, backend.py:1498-1519, because its later stages would execute the kernel
+    during shape propagation); ``TILELANG_FRONTEND_CONTINUE_AFTER_ATTENTION_FUSE=0``
+    restores the short-circuit.
+"""
+from __future__ import annotations
+
+import logging
+import math
+import operator
+import os
+from typing import List, Optional, Tuple
+
+import torch
+import torch.fx as fx
+from torch.fx import replace_pattern
+
+from .. import ops
+from .patterns import (
+    _heuristic_config,
+    scaled_dot_product_attention_pattern,
+    tilelang_flash_attn_replacement,
+    tilelang_flash_attn_wrapper,
+    tilelang_h2o_attention_wrapper,
+)
+
+log = logging.getLogger("heddle_b200")
+
+
+# ----------------------------------------------------------------------------------------
+# leaves inserted into FX graphs
+# ----------------------------------------------------------------------------------------
+@torch.fx.wrap
+def _tilelang_sdpa_direct(q, k, v, is_causal=None, scale=None):
+    """Attention on (B, H, S, D) tensors; returns a new (B, H, Sq, D) tensor of q's dtype.
+
+    ``is_causal=None`` keeps the reference's rule for a direct call — causal iff
+    Sq == Skv (Heddle/heddle/frontend/backend.py:215).  The graph rewrites in this module
+    always pass the value found in the graph.
+    """
+    if is_causal is None:
+        is_causal = q.shape[2] == k.shape[2]
+    return ops.fa_fwd(q, k, v, causal=bool(is_causal), softmax_scale=scale)
+
+
+@torch.fx.wrap
+def _tilelang_h2o_attention(q, k, v, is_causal=True, scale=None):
+    """FlashAttention (out + LSE) followed by the H2O column-sum of probabilities.
+
+    Returns ``(out[B,H,Sq,D], score[B,H,Skv] fp32)`` (backend.py:162-202; the reference
+    always uses the causal kernels here)."""
+    sm = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    out, lse = ops.fa_fwd(q, k, v, causal=bool(is_causal), softmax_scale=sm, return_lse=True)
+    score = ops.h2o_score(q, k, lse, causal=bool(is_causal), softmax_scale=sm)
+    return out, score
+
+
+_ATTENTION_LEAVES = (_tilelang_sdpa_direct, _tilelang_h2o_attention, tilelang_flash_attn_wrapper,
+                     tilelang_h2o_attention_wrapper)
+
+
+# ----------------------------------------------------------------------------------------
+# small FX helpers
+# ----------------------------------------------------------------------------------------
+def _name(node) -> str:
+    if not isinstance(node, fx.Node):
+        return ""
+    if node.op == "call_function":
+        return getattr(node.target, "__name__", None) or str(node.target)
+    if node.op == "call_method":
+        return str(node.target)
+    return ""
+
+
+def _arg(node: fx.Node, idx: int, kw: str, default=None):
+    if len(node.args) > idx:
+        return node.args[idx]
+    return node.kwargs.get(kw, default)
+
+
+def _is_softmax(node) -> bool:
+    return isinstance(node, fx.Node) and node.op in ("call_function", "call_method") and "softmax" in _name(node) \
+        and "log_softmax" not in _name(node)
+
+
+def _softmax_dim_is_last(node: fx.Node) -> bool:
+    dim = _arg(node, 1, "dim", -1)
+    if dim == -1:
+        return True
+    val = node.meta.get("example_value", None)
+    return val is not None and dim == val.dim() - 1
+
+
+def _skip_casts(node):
+    """Walk through dtype casts that do not change the math (``.float()``, ``.to(dtype)``)."""
+    while isinstance(node, fx.Node) and node.op == "call_method" and _name(node) in ("float", "to", "type", "contiguous"):
+        node = node.args[0]
+    return node
+
+
+def _shape_of(node) -> Optional[Tuple[int, ...]]:
+    if isinstance(node, fx.Node):
+        val = node.meta.get("example_value", node.meta.get("val", None))
+        if val is not None and hasattr(val, "shape"):
+            return tuple(int(s) for s in val.shape)
+        tm = node.meta.get("tensor_meta", None)
+        if tm is not None:
+            return tuple(int(s) for s in tm.shape)
+    return None
+
+
+def _is_neg_inf(x) -> bool:
+    return isinstance(x, (int, float)) and x == float("-inf")
+
+
+def _causal_mask_diagonal(mask: fx.Node) -> Optional[int]:
+    """If ``mask`` is ``triu(full(size, -inf), diagonal=d)`` return d, else None."""
+    mask = _skip_casts(mask)
+    if not isinstance(mask, fx.Node) or "triu" not in _name(mask):
+        return None
+    src = _skip_casts(mask.args[0]) if mask.args else None
+    diag = _arg(mask, 1, "diagonal", 0)
+    if not isinstance(diag, int) or not isinstance(src, fx.Node):
+        return None
+    if _name(src) in ("full", "full_like"):
+        fill = _arg(src, 1, "fill_value", None)
+        if _is_neg_inf(fill):
+            return diag
+    return None
+
+
+def _transposed_last_two(node) -> Optional[fx.Node]:
+    """If ``node`` is ``x.transpose(-2, -1)`` / ``x.mT`` / ``permute(0,1,3,2)`` return x."""
+    if not isinstance(node, fx.Node):
+        return None
+    nm = _name(node)
+    if nm == "transpose" and len(node.args) >= 3:
+        dims = {node.args[1], node.args[2]}
+        if dims in ({-2, -1}, {2, 3}, {-1, 2}, {-2, 3}):
+            return node.args[0]
+    if nm == "permute":
+        perm = node.args[1:] if len(node.args) > 2 else tuple(node.args[1])
+        if tuple(perm) == (0, 1, 3, 2):
+            return node.args[0]
+    if node.op == "call_function" and nm == "getattr" and len(node.args) == 2 and node.args[1] in ("mT", "mH"):
+        return node.args[0]
+    return None
+
+
+def _constant_scale(node: fx.Node) -> Optional[Tuple[fx.Node, float]]:
+    """``matmul / c`` or ``matmul * c`` with a Python constant: (matmul node, scale)."""
+    nm = _name(node)
+    if len(node.args) < 2:
+        return None
+    a, b = node.args[0], node.args[1]
+    if "div" in nm and isinstance(a, fx.Node) and isinstance(b, (int, float)) and b != 0:
+        return a, 1.0 / float(b)
+    if "mul" in nm:
+        if isinstance(a, fx.Node) and isinstance(b, (int, float)):
+            return a, float(b)
+        if isinstance(b, fx.Node) and isinstance(a, (int, float)):
+            return b, float(a)
+    return None
+
+
+class _AttentionMatch:
+    __slots__ = ("q", "k", "v", "scale", "causal", "softmax", "pv", "sum_user")
+
+
+def _match_attention(sm: fx.Node) -> Optional[_AttentionMatch]:
+    """Structural match anchored on a softmax over the last axis:
+    matmul(q, k^T) [*|/ const] [+ causal mask] -> softmax -> [cast] -> matmul(P, v)."""
+    if not _softmax_dim_is_last(sm):
+        return None
+    cur = _skip_casts(sm.args[0]) if sm.args else None
+    if not isinstance(cur, fx.Node):
+        return None
+    causal = False
+    mask_node = None
+    if _name(cur) in ("add", "iadd", "__add__"):
+        a, b = cur.args[0], cur.args[1]
+        if isinstance(b, fx.Node) and _causal_mask_diagonal(b) is not None:
+            mask_node, cur = b, _skip_casts(a)
+        elif isinstance(a, fx.Node) and _causal_mask_diagonal(a) is not None:
+            mask_node, cur = a, _skip_casts(b)
+        else:
+            return None  # an arbitrary additive mask: leave the graph alone
+    if not isinstance(cur, fx.Node):
+        return None
+    scale = 1.0
+    sc = _constant_scale(cur)
+    if sc is not None:
+        cur, scale = _skip_casts(sc[0]), sc[1]
+    elif _name(cur) in ("mul", "div", "truediv", "true_divide"):
+        return None  # a tensor-valued scale is not representable
+    if not isinstance(cur, fx.Node) or "matmul" not in _name(cur) or len(cur.args) < 2:
+        return None
+    q = cur.args[0]
+    k = _transposed_last_two(cur.args[1])
+    if not isinstance(q, fx.Node) or k is None:
+        return None
+    qs, ks = _shape_of(q), _shape_of(k)
+    if qs is None or ks is None or len(qs) != 4 or len(ks) != 4:
+        return None
+    if mask_node is not None:
+        if _causal_mask_diagonal(mask_node) != ks[2] - qs[2] + 1:
+            return None
+        causal = True
+    # forward: the probabilities feed exactly one matmul (as its first operand), optionally a sum
+    probs_users = []
+    frontier = [sm]
+    while frontier:
+        n = frontier.pop()
+        for u in n.users:
+            if u.op == "call_method" and _name(u) in ("to", "float", "type"):
+                frontier.append(u)
+            else:
+                probs_users.append((n, u))
+    pv = None
+    sum_user = None
+    for src, u in probs_users:
+        nm = _name(u)
+        if "matmul" in nm and len(u.args) >= 2 and u.args[0] is src and pv is None:
+            pv = u
+        elif nm == "sum" and sum_user is None:
+            sum_user = u
+        else:
+            return None  # the probabilities escape some other way (dropout, return value, ...)
+    if pv is None or not isinstance(pv.args[1], fx.Node):
+        return None
+    m = _AttentionMatch()
+    m.q, m.k, m.v, m.scale, m.causal, m.softmax, m.pv, m.sum_user = q, k, pv.args[1], scale, causal, sm, pv, sum_user
+    return m
+
+
+def _finish(gm: fx.GraphModule) -> None:
+    gm.graph.eliminate_dead_code()
+    gm.graph.lint()
+    gm.recompile()
+
+
+# ----------------------------------------------------------------------------------------
+# rewrite passes
+# ----------------------------------------------------------------------------------------
+def _replace_sdpa_op(gm: fx.GraphModule) -> bool:
+    """``F.scaled_dot_product_attention`` nodes -> ``_tilelang_sdpa_direct`` (backend.py:906).
+
+    Signature: (query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None).
+    Nodes with a mask or dropout are left in place."""
+    replaced = False
+    for node in list(gm.graph.nodes):
+        if node.op != "call_function" or "scaled_dot_product_attention" not in _name(node):
+            continue
+        q, k, v = _arg(node, 0, "query"), _arg(node, 1, "key"), _arg(node, 2, "value")
+        if not all(isinstance(t, fx.Node) for t in (q, k, v)):
+            continue
+        mask = _arg(node, 3, "attn_mask", None)
+        dropout = _arg(node, 4, "dropout_p", 0.0)
+        is_causal = _arg(node, 5, "is_causal", False)
+        scale = _arg(node, 6, "scale", None)
+        if mask is not None or dropout not in (0, 0.0) or not isinstance(is_causal, bool) \
+                or not (scale is None or isinstance(scale, (int, float))):
+            log.info("SDPA node %s keeps its eager form (mask / dropout / dynamic scale)", node.name)
+            continue
+        with gm.graph.inserting_before(node):
+            new = gm.graph.call_function(_tilelang_sdpa_direct, (q, k, v),
+                                         {"is_causal": is_causal, "scale": None if scale is None else float(scale)})
+        new.meta = dict(node.meta)
+        node.replace_all_uses_with(new)
+        gm.graph.erase_node(node)
+        replaced = True
+    if replaced:
+        _finish(gm)
+    return replaced
+
+
+def _replace_expanded_attention(gm: fx.GraphModule) -> bool:
+    """matmul -> scale -> [causal mask] -> softmax -> matmul written out by hand (backend.py:688).
+    With a ``sum`` over the query axis consuming the probabilities as well, the H2O leaf is used."""
+    replaced = False
+    for sm in list(gm.graph.nodes):
+        if not _is_softmax(sm):
+            continue
+        m = _match_attention(sm)
+        if m is None:
+            continue
+        kwargs = {"is_causal": m.causal, "scale": m.scale}
+        if m.sum_user is not None:
+            dim = _arg(m.sum_user, 1, "dim", None)
+            if dim not in (-2, 2) or _arg(m.sum_user, 2, "keepdim", False):
+                continue
+            with gm.graph.inserting_before(m.pv):
+                both = gm.graph.call_function(_tilelang_h2o_attention, (m.q, m.k, m.v), kwargs)
+                out = gm.graph.call_function(operator.getitem, (both, 0))
+                score = gm.graph.call_function(operator.getitem, (both, 1))
+            m.pv.replace_all_uses_with(out)
+            m.sum_user.replace_all_uses_with(score)
+        else:
+            with gm.graph.inserting_before(m.pv):
+                out = gm.graph.call_function(_tilelang_sdpa_direct, (m.q, m.k, m.v), kwargs)
+            out.meta = dict(m.pv.meta)
+            m.pv.replace_all_uses_with(out)
+        replaced = True
+    if replaced:
+        _finish(gm)
+    return replaced
+
+
+def try_fuse_h2o_attention(gm: fx.GraphModule) -> bool:
+    """H2O structure only: softmax -> {matmul(P, V), sum over queries} (backend.py:1316)."""
+    fused = False
+    for sm in list(gm.graph.nodes):
+        if not _is_softmax(sm):
+            continue
+        m = _match_attention(sm)
+        if m is None or m.sum_user is None:
+            continue
+        dim = _arg(m.sum_user, 1, "dim", None)
+        if dim not in (-2, 2) or _arg(m.sum_user, 2, "keepdim", False):
+            continue
+        with gm.graph.inserting_before(m.pv):
+            both = gm.graph.call_function(_tilelang_h2o_attention, (m.q, m.k, m.v),
+                                          {"is_causal": m.causal, "scale": m.scale})
+            out = gm.graph.call_function(operator.getitem, (both, 0))
+            score = gm.graph.call_function(operator.getitem, (both, 1))
+        m.pv.replace_all_uses_with(out)
+        m.sum_user.replace_all_uses_with(score)
+        fused = True
+    if fused:
+        _finish(gm)
+    return fused
+
+
+def _has_tilelang_wrapper_calls(gm: fx.GraphModule) -> bool:
+    return any(n.op == "call_function" and n.target in _ATTENTION_LEAVES for n in gm.graph.nodes)
+
+
+def _env_flag(name: str, default: str) -> bool:
+    return os.environ.get(name, default).strip() == "1"
+
+
+def tilelang_backend(gm: torch.fx.GraphModule, example_inputs: List[torch.Tensor]):
+    """Entry point for ``torch.compile(model, backend=tilelang_backend)`` (backend.py:1421).
+
+    1. attention rewrites (H2O structure, BSHD pattern, SDPA op, expanded attention);
+    2. GEMM + epilogue fusion of what surrounds it (linear + activation, SwiGLU,
+       RMSNorm-folded linears, RoPE on the QKV projection) onto the tcgen05 GEMM;
+    3. returns the rewritten ``GraphModule``.
+    """
+    enable_h2o = _env_flag("TILELANG_FRONTEND_ENABLE_H2O_FUSE", "1")
+    enable_fa = _env_flag("TILELANG_FRONTEND_ENABLE_FLASHATTN_PATTERN", "1")
+    continue_after = _env_flag("TILELANG_FRONTEND_CONTINUE_AFTER_ATTENTION_FUSE", "1")
+    enable_gemm = _env_flag("TILELANG_FRONTEND_EXECUTE_PARTITIONS", "1")
+    if os.environ.get("TILELANG_FRONTEND_PRINT_GRAPH", "0").strip() == "1":
+        print(gm.print_readable(print_output=False))
+
+    fused_attention = False
+    if enable_h2o:
+        fused_attention = try_fuse_h2o_attention(gm) or fused_attention
+    if enable_fa:
+        before = sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target is tilelang_flash_attn_wrapper)
+        replace_pattern(gm, scaled_dot_product_attention_pattern, tilelang_flash_attn_replacement)
+        after = sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target is tilelang_flash_attn_wrapper)
+        fused_sdpa = after > before
+        fused_sdpa = _replace_sdpa_op(gm) or fused_sdpa
+        if not fused_sdpa:
+            fused_sdpa = _replace_expanded_attention(gm)
+        fused_attention = fused_attention or fused_sdpa
+    log.info("attention fused: %s", fused_attention)
+
+    if enable_gemm and (continue_after or not fused_attention):
+        from .fusion import fuse_gemm_epilogues
+
+        n = fuse_gemm_epilogues(gm)
+        log.info("GEMM + epilogue groups fused: %d", n)
+    gm.recompile()
+    return gm

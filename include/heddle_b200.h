@@ -131,8 +131,11 @@ int hb_h2o_score(const hb_h2o_args* args);
  *   ROWSCALE    out = row_scale[m] * acc   (RMSNorm with gamma folded into w)
  *   ROPE        rotate-half RoPE on head_dim-wide column groups,
  *               cos/sin tables [rope_seq, head_dim/2] fp32, position = m % rope_seq
- * Optional operands: row_scale (fp32 [M]) may accompany any epilogue and is applied
- * first; residual ([M, N_out], out dtype) is added last.
+ * Optional operands, any epilogue: row_scale (fp32 [M]) multiplies the accumulator
+ * first; bias ([N], dtype) is added next, before the activation / gate / rotation;
+ * residual ([M, N_out], dtype) is added last.
+ * Constraints: K, N_out, lda, ldw, ldo, ldr multiples of 8 elements; 16-byte aligned
+ * pointers; ROPE needs head_dim in {64, 128, 256} dividing N and rope_cols.
  */
 typedef enum hb_epilogue {
   HB_EPI_NONE = 0,
@@ -154,6 +157,7 @@ typedef struct hb_gemm_args {
   int32_t dtype; /* HB_BF16 or HB_FP16 */
   int32_t epilogue;
   const float* row_scale;  /* optional fp32 [M] */
+  const void* bias;        /* optional [N] */
   const void* residual;    /* optional [M, N_out], row stride ldr */
   int64_t ldr;
   const float* rope_cos;   /* ROPE: [rope_seq, head_dim/2] */
