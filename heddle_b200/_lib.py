@@ -77,7 +77,7 @@ class GemmArgs(C.Structure):
 
 # every symbol include/heddle_b200.h declares
 EXPORTS = (
-    "hb_fa_fwd", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_status_word", "hb_version",
+    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_status_word", "hb_version",
     "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma",
 )
 
@@ -97,6 +97,8 @@ def load() -> C.CDLL:
     lib = C.CDLL(str(path))
     lib.hb_fa_fwd.argtypes = [C.POINTER(FaArgs)]
     lib.hb_fa_fwd.restype = C.c_int
+    lib.hb_fa_fwd_noalloc.argtypes = [C.POINTER(FaArgs)]
+    lib.hb_fa_fwd_noalloc.restype = C.c_int
     lib.hb_h2o_score.argtypes = [C.POINTER(H2oArgs)]
     lib.hb_h2o_score.restype = C.c_int
     lib.hb_gemm_epilogue.argtypes = [C.POINTER(GemmArgs)]

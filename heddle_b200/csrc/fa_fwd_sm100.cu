@@ -124,6 +124,126 @@ static int fa_fwd_impl(const hb_fa_args* a) {
 }
 
 // ------------------------------------------------------------------------------------
+// hb_fa_fwd_noalloc: the same kernel for callers that must not allocate device memory
+// ------------------------------------------------------------------------------------
+// hb_fa_fwd keeps its device-side status word (the scratch the kernel's bounded waits
+// report into) in memory it obtains with cudaMalloc on the first call per device.  A
+// host that runs under a fixed memory budget, forbids allocation after start-up, or is
+// in the middle of a stream capture cannot make that call.  This variant keeps the
+// scratch in the array below instead: it is part of the library image, so every GPU
+// that loads the library holds kFaNoallocScratchBytes of it until the process exits.
+constexpr size_t kFaNoallocScratchBytes = 256;
+static __device__ __align__(256) unsigned char g_fa_noalloc_scratch[kFaNoallocScratchBytes];
+
+// What one launch needs from the scratch: the status word.
+constexpr size_t kFaScratchNeeded = sizeof(uint32_t);
+
+// Device address of the scratch array per device.  In host code the array's name is only
+// a stand-in for the symbol, never a device pointer; the address the kernel must be given
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+static void* g_fa_noalloc_ptr[64] = {};
+
+static int fa_fwd_noalloc_impl(const hb_fa_args* a) {
+  if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: args is NULL");
+  if (a->B < 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq < 0 || a->Skv < 0 || a->D <= 0)
+    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: negative or zero extent (B=%d Hq=%d Hkv=%d Sq=%d Skv=%d D=%d)",
+                     a->B, a->Hq, a->Hkv, a->Sq, a->Skv, a->D);
+  if (a->Hq % a->Hkv != 0)
+    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
+  if (a->dtype != HB_BF16 && a->dtype != HB_FP16)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: dtype %d not supported (bf16, fp16)", a->dtype);
+  if (a->D != 64 && a->D != 128)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: head_dim %d not supported (64 or 128)", a->D);
+  if (kFaScratchNeeded > kFaNoallocScratchBytes)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: the kernel needs %zu bytes of scratch, the static array holds %zu",
+                     kFaScratchNeeded, kFaNoallocScratchBytes);
+  if (a->B == 0 || a->Sq == 0) return HB_OK;
+  if (a->Skv == 0) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: Skv is 0 (softmax over an empty set)");
+  if (a->causal && a->Skv < a->Sq)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: causal attention needs Skv >= Sq");
+  if (a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr)
+    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: q, k, v and o must be non-NULL");
+  const size_t es = dtype_size(a->dtype);
+  if ((reinterpret_cast<uintptr_t>(a->o) & 15u) != 0 || ((a->o_stride_s * es) & 15u) != 0 ||
+      ((a->o_stride_h * es) & 15u) != 0 || ((a->o_stride_b * es) & 15u) != 0)
+    return set_error(HB_ERR_ALIGN, "hb_fa_fwd_noalloc: o and its strides must be 16-byte aligned");
+  // The work list is indexed with 32-bit integers; this is the largest problem one launch takes.
+  const int nqb = (a->Sq + 2 * kTileM - 1) / (2 * kTileM);
+  const int npairs = (nqb + 1) / 2;
+  const long long total = (long long)a->B * a->Hq * npairs;
+  if (total > 0x7fffffffLL)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: problem too large (%lld query blocks, limit %d)", total,
+                     0x7fffffff);
+
+  DeviceInfo info;
+  int rc = get_device_info_noalloc(&info);
+  if (rc != HB_OK) return rc;
+  if (info.device >= 64) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: device index %d out of range", info.device);
+  if (g_fa_noalloc_ptr[info.device] == nullptr) {
+    // first call on this device: resolve the array's device address (no allocation)
+    void* ptr = nullptr;
+    cudaError_t err = cudaGetSymbolAddress(&ptr, g_fa_noalloc_scratch);
+    if (err != cudaSuccess || ptr == nullptr)
+      return set_error(HB_ERR_CUDA, "hb_fa_fwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+    g_fa_noalloc_ptr[info.device] = ptr;
+  }
+  uint32_t* status = static_cast<uint32_t*>(g_fa_noalloc_ptr[info.device]);
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  // the array keeps the previous call's contents: the status word must start at zero
+  HB_CUDA_CHECK(cudaMemsetAsync(status, 0, kFaScratchNeeded, stream));
+
+  FaParams p;
+  memset(&p, 0, sizeof(p));
+  const CUtensorMapDataType dt =
+      a->dtype == HB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const uint32_t box[4] = {64, (uint32_t)kTileM, 1, 1};
+  {
+    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Sq, (uint64_t)a->Hq, (uint64_t)a->B};
+    const uint64_t str[3] = {(uint64_t)a->q_stride_s * es, (uint64_t)a->q_stride_h * es, (uint64_t)a->q_stride_b * es};
+    rc = encode_tensor_map(&p.tm_q, dt, 4, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  }
+  {
+    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Skv, (uint64_t)a->Hkv, (uint64_t)a->B};
+    const uint64_t str[3] = {(uint64_t)a->k_stride_s * es, (uint64_t)a->k_stride_h * es, (uint64_t)a->k_stride_b * es};
+    rc = encode_tensor_map(&p.tm_k, dt, 4, a->k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  }
+  {
+    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Skv, (uint64_t)a->Hkv, (uint64_t)a->B};
+    const uint64_t str[3] = {(uint64_t)a->v_stride_s * es, (uint64_t)a->v_stride_h * es, (uint64_t)a->v_stride_b * es};
+    rc = encode_tensor_map(&p.tm_v, dt, 4, a->v, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  }
+  p.o = a->o;
+  p.lse = a->lse;
+  p.status = status;
+  p.o_sb = a->o_stride_b;
+  p.o_sh = a->o_stride_h;
+  p.o_ss = a->o_stride_s;
+  p.B = a->B;
+  p.Hq = a->Hq;
+  p.Hkv = a->Hkv;
+  p.Sq = a->Sq;
+  p.Skv = a->Skv;
+  p.group = a->Hq / a->Hkv;
+  p.causal = a->causal ? 1 : 0;
+  p.nqb = nqb;
+  p.npairs = npairs;
+  p.total_pairs = (int)total;
+  p.nkv = (a->Skv + kTileN - 1) / kTileN;
+  const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->D);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int grid = (int)std::min<long long>(total, info.sm_count);
+  if (a->dtype == HB_BF16) {
+    return a->D == 128 ? launch_fa<__nv_bfloat16, 128>(p, grid, info.smem_optin, stream)
+                       : launch_fa<__nv_bfloat16, 64>(p, grid, info.smem_optin, stream);
+  }
+  return a->D == 128 ? launch_fa<__half, 128>(p, grid, info.smem_optin, stream)
+                     : launch_fa<__half, 64>(p, grid, info.smem_optin, stream);
+}
+
+// ------------------------------------------------------------------------------------
 // one-tile tcgen05 probe
 // ------------------------------------------------------------------------------------
 struct alignas(64) UmmaProbeParams {
@@ -278,6 +398,11 @@ extern "C" {
 int hb_fa_fwd(const hb_fa_args* args) {
   hb::clear_error();
   return hb::fa_fwd_impl(args);
+}
+
+int hb_fa_fwd_noalloc(const hb_fa_args* args) {
+  hb::clear_error();
+  return hb::fa_fwd_noalloc_impl(args);
 }
 
 int hb_debug_umma(int mode, const void* a, const void* b, float* out, int32_t kn, int32_t dtype, void* stream) {

@@ -63,6 +63,31 @@ int get_device_state(DeviceState** out) {
   return HB_OK;
 }
 
+int get_device_info_noalloc(DeviceInfo* out) {
+  int dev = -1;
+  HB_CUDA_CHECK(cudaGetDevice(&dev));
+  int major = 0, minor = 0;
+  HB_CUDA_CHECK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  HB_CUDA_CHECK(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
+  HB_CUDA_CHECK(cudaDeviceGetAttribute(&out->sm_count, cudaDevAttrMultiProcessorCount, dev));
+  HB_CUDA_CHECK(cudaDeviceGetAttribute(&out->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+  out->device = dev;
+  out->cc = major * 10 + minor;
+  if (out->cc != 100)
+    return set_error(HB_ERR_UNSUPPORTED, "device %d has compute capability %d.%d; this library is built for sm_100a only",
+                     dev, major, minor);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    HB_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr)
+      return set_error(HB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  return HB_OK;
+}
+
 int encode_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
   if (g_encode == nullptr) return set_error(HB_ERR_CUDA, "tensor-map encoder not initialised");

@@ -33,6 +33,16 @@ struct DeviceState {
 // Lazily created state of the CURRENT device (mutex-guarded).  Returns an hb_status.
 int get_device_state(DeviceState** out);
 
+// Device facts for entry points that must not allocate: attribute queries and the
+// driver entry point only (no cudaMalloc, no per-device state is created).
+struct DeviceInfo {
+  int device = -1;
+  int sm_count = 0;
+  int smem_optin = 0;
+  int cc = 0;
+};
+int get_device_info_noalloc(DeviceInfo* out);
+
 // 2-D .. 4-D tiled tensor map with 128-byte swizzle, zero fill out of bounds.
 //   dims[i]     extent of dimension i in elements (dimension 0 is contiguous)
 //   strides[i]  byte stride of dimension i+1

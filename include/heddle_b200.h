@@ -94,6 +94,30 @@ typedef struct hb_fa_args {
 int hb_fa_fwd(const hb_fa_args* args);
 
 /*
+ * hb_fa_fwd for callers that cannot allocate device memory.  No counterpart in the
+ * reference (its kernels and their buffers are created by TileLang's JIT at run time).
+ *
+ * Who needs it: hb_fa_fwd obtains the device-side status word its kernel reports into
+ * with cudaMalloc on the first call per device.  A host process that runs under a fixed
+ * memory budget, forbids allocation once it has started serving, or calls from inside a
+ * region where cudaMalloc is not permitted cannot make that first call.  This entry
+ * point computes exactly the same result with the same kernel, but keeps that scratch
+ * in a static device array compiled into the library (256 bytes; every GPU that loads
+ * the library holds it until the process exits) and calls no cudaMalloc, cudaFree or
+ * other allocating routine.  The caller still passes q, k, v, o and lse.
+ *
+ * Set-up: the first call on each device resolves the array's device address
+ * (cudaGetSymbolAddress, with that device current).  Make that first call outside any
+ * stream capture.  Limits: bf16 / fp16 only; at most 2^31-1 query blocks of 256 rows
+ * (B * Hq * ceil(ceil(Sq/256)/2)) per call, larger problems are rejected with
+ * HB_ERR_UNSUPPORTED.  All calls on a device share the one array, which keeps the last
+ * call's contents; each call clears its status word on `stream` before the kernel runs,
+ * so two calls whose kernels overlap on the GPU (different streams) race on it — issue
+ * them on one stream or order them with events.
+ */
+int hb_fa_fwd_noalloc(const hb_fa_args* args);
+
+/*
  * H2O score:  score[b,h,k] = sum_q exp(scaled masked score[q,k] - LSE[q])
  * Replaces Heddle/heddle/tileop/h2o_attention.py:27-136 (h2o_score), called from
  * backend.py:162-202 (_tilelang_h2o_attention).  lse is the natural-log LSE that
