@@ -109,3 +109,108 @@ def debug_umma(mode: int, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         _lib.check(_lib.load().hb_debug_umma(mode, a.data_ptr(), b.data_ptr(), out.data_ptr(), kn,
                                              _DTYPES[a.dtype], _stream_ptr(a.device)))
     return out
+
+
+def gemm_epilogue(a: torch.Tensor, w: torch.Tensor, epilogue: str = "none", *,
+                  bias: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
+                  residual: Optional[torch.Tensor] = None,
+                  rope: Optional[Tuple[torch.Tensor, torch.Tensor, int, int]] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``epilogue(a @ w.T)`` through ``hb_gemm_epilogue``.
+
+    ``a`` is (..., K) and is viewed as [M, K]; ``w`` is [N, K] in nn.Linear layout
+    ([2*N_out, K] = cat([Wg, Wu]) for "swiglu").  ``row_scale`` fp32 [M]; ``bias`` [N];
+    ``residual`` (..., N_out); ``rope`` = (cos [S, hd/2] fp32, sin, head_dim, rope_cols)
+    with position = row index mod S.  Returns (..., N_out) in a's dtype.
+    """
+    _require_cuda(a, w, bias, row_scale, residual)
+    if a.dtype not in (torch.bfloat16, torch.float16) or w.dtype != a.dtype:
+        raise TypeError(f"gemm_epilogue needs matching bf16/fp16 operands, got {a.dtype} and {w.dtype}")
+    if epilogue not in _lib.EPILOGUES:
+        raise ValueError(f"unknown epilogue {epilogue!r}")
+    K = a.shape[-1]
+    lead = a.shape[:-1]
+    a2 = a.reshape(-1, K)
+    if a2.stride(-1) != 1:
+        a2 = a2.contiguous()
+    if w.dim() != 2 or w.shape[1] != K:
+        raise ValueError(f"weight shape {tuple(w.shape)} does not match K={K}")
+    if w.stride(-1) != 1:
+        w = w.contiguous()
+    M, N = a2.shape[0], w.shape[0]
+    n_out = N // 2 if epilogue == "swiglu" else N
+    if out is None:
+        out2 = torch.empty((M, n_out), dtype=a.dtype, device=a.device)
+    else:
+        out2 = out.reshape(-1, n_out)
+        if out2.data_ptr() != out.data_ptr() or out2.stride(-1) != 1:
+            raise ValueError("out must be viewable as a row-major [M, N_out] matrix")
+    g = _lib.GemmArgs()
+    g.a, g.w, g.out = a2.data_ptr(), w.data_ptr(), out2.data_ptr()
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldw, g.ldo = a2.stride(0), w.stride(0), out2.stride(0)
+    g.dtype = _DTYPES[a.dtype]
+    g.epilogue = _lib.EPILOGUES[epilogue]
+    keep = []
+    if row_scale is not None:
+        rs = row_scale.reshape(-1).to(torch.float32).contiguous()
+        if rs.numel() != M:
+            raise ValueError("row_scale must have one entry per row")
+        keep.append(rs)
+        g.row_scale = rs.data_ptr()
+    if bias is not None:
+        b = bias.to(a.dtype).contiguous()
+        if b.numel() != N:
+            raise ValueError("bias must have N entries")
+        keep.append(b)
+        g.bias = b.data_ptr()
+    if residual is not None:
+        r2 = residual.reshape(-1, n_out)
+        if r2.dtype != a.dtype or r2.stride(-1) != 1:
+            r2 = r2.to(a.dtype).contiguous()
+        keep.append(r2)
+        g.residual, g.ldr = r2.data_ptr(), r2.stride(0)
+    if epilogue == "rope":
+        if rope is None:
+            raise ValueError("epilogue 'rope' needs rope=(cos, sin, head_dim, rope_cols)")
+        cos, sin, hd, rope_cols = rope
+        cos = cos.to(torch.float32).contiguous()
+        sin = sin.to(torch.float32).contiguous()
+        _require_cuda(cos, sin)
+        keep += [cos, sin]
+        g.rope_cos, g.rope_sin = cos.data_ptr(), sin.data_ptr()
+        g.rope_seq, g.head_dim, g.rope_cols = cos.shape[0], int(hd), int(rope_cols)
+    g.stream = _stream_ptr(a.device)
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.load().hb_gemm_epilogue(C.byref(g)))
+    return out2.reshape(*lead, n_out) if out is None else out
+
+
+def rms_rowstat(x: torch.Tensor, residual: Optional[torch.Tensor] = None, eps: float = 1e-5,
+                write_sum: bool = False) -> "Tuple[Optional[torch.Tensor], torch.Tensor]":
+    """Row statistic of RMSNorm fused with the residual add (``hb_rms_rowstat``).
+
+    Returns (y, rstd): y = x + residual in x's dtype (None unless ``write_sum`` or a
+    residual is given), rstd fp32 of shape x.shape[:-1]."""
+    _require_cuda(x, residual)
+    N = x.shape[-1]
+    x2 = x.reshape(-1, N)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    r2 = None
+    if residual is not None:
+        r2 = residual.reshape(-1, N)
+        if r2.stride() != x2.stride() or r2.dtype != x.dtype:
+            r2 = r2.to(x.dtype).contiguous()
+            x2 = x2.contiguous()
+    y = torch.empty_like(x2) if (write_sum or residual is not None) else None
+    if y is not None and y.stride() != x2.stride():
+        x2 = x2.contiguous()
+        y = torch.empty_like(x2)
+    rstd = torch.empty((M,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().hb_rms_rowstat(x2.data_ptr(), r2.data_ptr() if r2 is not None else None,
+                                              y.data_ptr() if y is not None else None, rstd.data_ptr(), M, N,
+                                              x2.stride(0), float(eps), _DTYPES[x.dtype], _stream_ptr(x.device)))
+    return (y.reshape(x.shape) if y is not None else None), rstd.reshape(x.shape[:-1])

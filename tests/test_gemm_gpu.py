@@ -1,0 +1,125 @@
+"""Parity of the tcgen05 GEMM + epilogue kernels (through the C ABI) with the CPU oracle
+and the reference-generated fixtures.  Tolerance: the output is rounded to bf16/fp16, so
+errors are measured relative to the magnitude of the result (2e-2 absolute at unit scale)."""
+import pytest
+import torch
+
+from oracle import attention_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(built_lib):
+    from heddle_b200 import ops as _ops
+    return _ops
+
+
+def _close(out, ref, tol=2e-2):
+    scale = max(1.0, ref.float().abs().max().item())
+    err = (out.float().cpu() - ref.float()).abs().max().item()
+    assert err <= tol * scale, (err, scale)
+
+
+def _mk(M, N, K, seed, dtype=torch.bfloat16, wscale=0.05):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(M, K, generator=g).to(dtype)
+    w = (torch.randn(N, K, generator=g) * wscale).to(dtype)
+    return a, w
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (256, 512, 128), (96, 192, 128),
+                                   (1000, 328, 200), (130, 264, 72), (2048, 1024, 1024), (8, 8, 8)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_plain_gemm(ops, M, N, K, dtype):
+    a, w = _mk(M, N, K, seed=M + N + K, dtype=dtype)
+    out = ops.gemm_epilogue(a.cuda(), w.cuda())
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    _close(out, O.gemm_epilogue(a, w, "none"), tol=1e-2)
+
+
+@pytest.mark.parametrize("act", ["silu", "relu", "gelu_tanh", "sigmoid", "tanh"])
+def test_unary_epilogues(ops, act):
+    a, w = _mk(300, 520, 256, seed=5)
+    out = ops.gemm_epilogue(a.cuda(), w.cuda(), act)
+    _close(out, O.gemm_epilogue(a, w, act), tol=1e-2)
+
+
+def test_reference_fixture_epilogues(ops, golden):
+    gm = golden["gemm"]
+    g = torch.Generator().manual_seed(gm["seed"])
+    x = torch.randn(96, 128, generator=g).to(torch.bfloat16)
+    w = (torch.randn(192, 128, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(192, 128, generator=g) * 0.05).to(torch.bfloat16)
+    for act in ("none", "silu", "relu", "gelu_tanh", "sigmoid", "tanh"):
+        _close(ops.gemm_epilogue(x.cuda(), w.cuda(), act), gm[act], tol=1e-2)
+    _close(ops.gemm_epilogue(x.cuda(), torch.cat([w, w2]).cuda(), "swiglu"), gm["swiglu"], tol=1e-2)
+
+
+@pytest.mark.parametrize("M,N_out,K", [(256, 128, 128), (500, 344, 264), (1024, 1408, 512)])
+def test_swiglu(ops, M, N_out, K):
+    a, w = _mk(M, 2 * N_out, K, seed=9)
+    out = ops.gemm_epilogue(a.cuda(), w.cuda(), "swiglu")
+    assert out.shape == (M, N_out)
+    _close(out, O.gemm_epilogue(a, w, "swiglu"), tol=1e-2)
+
+
+def test_row_scale_bias_residual(ops):
+    a, w = _mk(384, 512, 320, seed=13)
+    g = torch.Generator().manual_seed(14)
+    rs = torch.rand(384, generator=g) + 0.5
+    bias = torch.randn(512, generator=g).to(torch.bfloat16)
+    res = torch.randn(384, 512, generator=g).to(torch.bfloat16)
+    out = ops.gemm_epilogue(a.cuda(), w.cuda(), "silu", row_scale=rs.cuda(), bias=bias.cuda(), residual=res.cuda())
+    acc = (a.float() @ w.float().t()) * rs[:, None] + bias.float()
+    ref = O.epilogue_fp32(acc, "silu") + res.float()
+    _close(out, ref, tol=1e-2)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_rope_epilogue(ops, hd):
+    B, S, H = 2, 96, 3
+    a, w = _mk(B * S, 3 * H * hd, 256, seed=17)
+    cos, sin = O.rope_tables(S, hd)
+    out = ops.gemm_epilogue(a.cuda(), w.cuda(), "rope", rope=(cos.cuda(), sin.cuda(), hd, 2 * H * hd))
+    ref = O.gemm_epilogue(a, w, "rope", rope=(cos, sin, hd, 2 * H * hd))
+    _close(out, ref, tol=1e-2)
+
+
+def test_rms_rowstat_and_folded_rmsnorm_linear(ops):
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(200, 512, generator=g).to(torch.bfloat16)
+    r = torch.randn(200, 512, generator=g).to(torch.bfloat16)
+    gamma = (torch.rand(512, generator=g) + 0.5)
+    w = (torch.randn(384, 512, generator=g) * 0.05).to(torch.bfloat16)
+    y, rstd = ops.rms_rowstat(x.cuda(), r.cuda(), eps=1e-5)
+    y_ref, rstd_ref = O.rms_rowstat(x, r, 1e-5)
+    assert torch.equal(y.cpu(), y_ref)
+    assert (rstd.cpu() - rstd_ref).abs().max().item() <= 1e-5 * rstd_ref.abs().max().item() + 1e-6
+    # RMSNorm(y) @ w.T  ==  rstd * (y @ (gamma * w).T)
+    wf = (w.float() * gamma[None, :]).to(torch.bfloat16)
+    out = ops.gemm_epilogue(y, wf.cuda(), row_scale=rstd)
+    ref = (y_ref.float() * rstd_ref[:, None] * gamma[None, :]) @ w.float().t()
+    _close(out, ref, tol=2e-2)
+    _, rstd_only = ops.rms_rowstat(x.cuda(), None, eps=1e-5)
+    assert (rstd_only.cpu() - O.rms_rowstat(x, None, 1e-5)[1]).abs().max().item() <= 1e-5
+
+
+def test_full_size_projection_properties(ops):
+    """Config-5 sized GEMM (M=16384, N=4096, K=4096): linearity and a sampled-row oracle check."""
+    M, N, K = 16384, 4096, 4096
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(M, K, generator=gen, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+    out = ops.gemm_epilogue(a, w)
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    rows = torch.tensor([0, 1, 127, 128, 4097, 16383], device="cuda")
+    ref = a[rows].float() @ w.float().t()
+    assert (out[rows].float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    # scaling A by 2 (exact in bf16) doubles the result exactly
+    out2 = ops.gemm_epilogue(a * 2, w)
+    assert torch.equal(out2.float(), out.float() * 2)
+    # deterministic
+    assert torch.equal(ops.gemm_epilogue(a, w), out)
