@@ -40,6 +40,10 @@ static int launch_fa(const FaParams& p, int grid, int smem_optin, cudaStream_t s
   return HB_OK;
 }
 
+#ifdef HB_FA_TRACE
+static unsigned long long* g_trace_ptr = nullptr;
+#endif
+
 static int fa_fwd_impl(const hb_fa_args* a) {
   if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: args is NULL");
   if (a->B < 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq < 0 || a->Skv < 0 || a->D <= 0)
@@ -96,6 +100,9 @@ static int fa_fwd_impl(const hb_fa_args* a) {
   p.o = a->o;
   p.lse = a->lse;
   p.status = st->status_word;
+#ifdef HB_FA_TRACE
+  p.trace = g_trace_ptr;
+#endif
   p.o_sb = a->o_stride_b;
   p.o_sh = a->o_stride_h;
   p.o_ss = a->o_stride_s;
@@ -399,6 +406,14 @@ int hb_fa_fwd(const hb_fa_args* args) {
   hb::clear_error();
   return hb::fa_fwd_impl(args);
 }
+
+#ifdef HB_FA_TRACE
+// tracing builds only: device buffer of 16 regions x 4096 x 8 bytes, zeroed by the caller
+int hb_debug_set_trace(void* ptr) {
+  hb::g_trace_ptr = static_cast<unsigned long long*>(ptr);
+  return 0;
+}
+#endif
 
 int hb_fa_fwd_noalloc(const hb_fa_args* args) {
   hb::clear_error();

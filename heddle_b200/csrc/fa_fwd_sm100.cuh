@@ -33,6 +33,26 @@ constexpr int kTileM = 128;  // query rows per softmax warpgroup
 constexpr int kTileN = 128;  // keys per step
 constexpr float kRescaleThreshold = 8.0f;  // log2 units; below it the stale max is kept
 
+// Optional phase tracing (compiled in with -DHB_FA_TRACE only): lane 0 of selected warps of
+// CTA 0 appends (clock64 << 8 | code) records to a caller-provided buffer, 4096 slots per region.
+#ifdef HB_FA_TRACE
+#define HB_TRACE(p, region, code)                                                          \
+  do {                                                                                     \
+    if ((p).trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {              \
+      unsigned long long* t_ = (p).trace + (region) * 4096;                                \
+      const unsigned long long n_ = t_[0];                                                 \
+      if (n_ < 4094) {                                                                     \
+        t_[1 + n_] = (static_cast<unsigned long long>(clock64()) << 8) | (code);           \
+        t_[0] = n_ + 1;                                                                    \
+      }                                                                                    \
+    }                                                                                      \
+  } while (0)
+#else
+#define HB_TRACE(p, region, code) \
+  do {                            \
+  } while (0)
+#endif
+
 enum FaRole : uint32_t { kRoleSoftmax = 1, kRoleCorrection = 2, kRoleMma = 3, kRoleTma = 4, kRoleDrain = 5 };
 
 struct alignas(64) FaParams {
@@ -42,6 +62,7 @@ struct alignas(64) FaParams {
   void* o;
   float* lse;
   uint32_t* status;
+  unsigned long long* trace;  // phase trace buffer (tracing builds only), else NULL
   long long o_sb, o_sh, o_ss;  // elements
   int B, Hq, Hkv, Sq, Skv;
   int group;        // Hq / Hkv
@@ -126,14 +147,17 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
       float m = -INFINITY, l = 0.f;
 
       for (int j = 0; j < n; ++j) {
+        HB_TRACE(p, warp, 0);
         if (!mbar_wait_warp(&s.s_full[i], s_cnt & 1, ctx, kRoleSoftmax)) return;
         ++s_cnt;
         tc_fence_after();
+        HB_TRACE(p, warp, 1);
 
         uint32_t v[kTileN];  // fp32 scores of this row, as raw bits
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, &v[c * 32]);
         tmem_wait_ld();
+        HB_TRACE(p, warp, 2);
 
         const int col0 = j * kTileN;
         const bool need_mask = (col0 + kTileN > p.Skv) || (p.causal && (col0 + kTileN - 1 > tile_pos0));
@@ -176,6 +200,7 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.corr_full[i]);
         ++c_cnt;
+        HB_TRACE(p, warp, 3);
 
         float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
@@ -198,11 +223,13 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
           tmem_st16(tS + q * 16, pk);
         }
         l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+        HB_TRACE(p, warp, 4);
 
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.p_full[i]);
+        HB_TRACE(p, warp, 5);
       }
 
       // final row statistics for the epilogue
@@ -239,6 +266,7 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
           if (j >= it.n[i]) continue;
           if (!mbar_wait_warp(&s.corr_full[i], c_cnt[i] & 1, ctx, kRoleCorrection)) return;
           ++c_cnt[i];
+          HB_TRACE(p, warp, 20 + i);
           const float a = s.alpha[i][row];
           __syncwarp();
           if (lane == 0) mbar_arrive(&s.corr_empty[i]);
@@ -259,6 +287,7 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&s.p_full[i]);
+          HB_TRACE(p, warp, 22 + i);
         }
       }
 
@@ -319,92 +348,109 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s,
   constexpr uint32_t idesc_qk = make_idesc(kFmt, kTileM, kTileN, 0, 0);
   constexpr uint32_t idesc_pv = make_idesc(kFmt, kTileM, D, 0, 1);
   constexpr uint32_t kHalfBytes = kTileM * 128;  // one 64-element-wide, 128-row sub-tile
-  uint32_t kv_cons = 0, q_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
-
-  // Descriptor constants: only the 14-bit start-address field changes per MMA.
-  constexpr uint64_t kDescK = (uint64_t(16 >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-  constexpr uint64_t kDescV =
-      (uint64_t(kHalfBytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-  const uint32_t q_base = smem_u32(s.q[0]) >> 4;
-  const uint32_t kv_base = smem_u32(s.kv[0]) >> 4;
+  // Shared-memory descriptors: the high word (SBO = 1024 B, version 1, SWIZZLE_128B) is constant;
+  // the low word is (address >> 4) | (LBO >> 4) << 16 and only its address field moves per MMA.
+  constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  constexpr uint32_t kLboK = (16u >> 4) << 16;
+  constexpr uint32_t kLboV = (kHalfBytes >> 4) << 16;
   constexpr uint32_t kTile16 = FaSmem<D, NS>::kTileBytes >> 4;
+  const uint32_t q_lo = (smem_u32(s.q[0]) >> 4) | kLboK;
+  const uint32_t kv_lo = smem_u32(s.kv[0]) >> 4;
+  auto desc = [](uint32_t lo) -> uint64_t { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
 
   auto issue_qk = [&](int i, uint32_t slot) {
-    const uint32_t qa = q_base + static_cast<uint32_t>(i) * kTile16;
-    const uint32_t ka = kv_base + slot * kTile16;
+    const uint32_t qa = q_lo + static_cast<uint32_t>(i) * kTile16;
+    const uint32_t ka = (kv_lo + slot * kTile16) | kLboK;
     const uint32_t d_tmem = tmem + static_cast<uint32_t>(i * kTileN);
-#pragma unroll 1
+#pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       // 16 elements (32 bytes) per step inside a 64-element sub-tile, then the next sub-tile
-      const uint32_t off = (static_cast<uint32_t>(kk >> 2) * kHalfBytes + static_cast<uint32_t>(kk & 3) * 32u) >> 4;
-      umma_ss_f16(d_tmem, kDescK | (qa + off), kDescK | (ka + off), idesc_qk, kk > 0 ? 1u : 0u);
+      constexpr uint32_t kSub = kHalfBytes >> 4;
+      const uint32_t off = static_cast<uint32_t>(kk >> 2) * kSub + static_cast<uint32_t>(kk & 3) * 2u;
+      umma_ss_f16(d_tmem, desc(qa + off), desc(ka + off), idesc_qk, kk > 0 ? 1u : 0u);
     }
   };
-  auto issue_pv = [&](int i, uint32_t slot, bool accumulate) {
-    const uint32_t va = kv_base + slot * kTile16;
+  auto issue_pv = [&](int i, uint32_t slot, uint32_t accumulate) {
+    const uint32_t va = (kv_lo + slot * kTile16) | kLboV;
     const uint32_t d_tmem = tmem + 256u + static_cast<uint32_t>(i * 128);
     const uint32_t a_tmem = tmem + static_cast<uint32_t>(i * kTileN);
-#pragma unroll 1
+#pragma unroll
     for (int kk = 0; kk < kTileN / 16; ++kk) {
       // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2048 bytes) of V
-      umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), kDescV | (va + static_cast<uint32_t>(kk) * 128u),
-                  idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+      umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), desc(va + static_cast<uint32_t>(kk) * 128u), idesc_pv,
+                  kk > 0 ? 1u : accumulate);
     }
   };
+
+  // consumer side of the K/V ring
+  uint32_t slot = 0, phase = 0;
+  auto advance = [&]() {
+    if (++slot == NS) {
+      slot = 0;
+      phase ^= 1;
+    }
+  };
+  uint32_t q_phase = 0, p_phase = 0;  // bit i = parity of tile i's barrier
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
     for (int half = 0; half < 2; ++half) {
       FaItem it;
       if (!fa_get_item(p, g, half, it)) continue;
-      const int nmax = max(it.n[0], it.n[1]);
+      const int n0 = it.n[0], n1 = it.n[1];
+      const int nmax = max(n0, n1);
 
       // step 0 scores
-      uint32_t slot_k = kv_cons % NS;
-      if (!mbar_wait(&s.kv_full[slot_k], (kv_cons / NS) & 1, ctx, kRoleMma)) return;
-      ++kv_cons;
-#pragma unroll
+      uint32_t slot_k = slot;
+      if (!mbar_wait(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
+      advance();
+#pragma unroll 1
       for (int i = 0; i < 2; ++i) {
-        if (it.n[i] == 0) continue;
-        if (!mbar_wait(&s.q_full[i], q_cnt[i] & 1, ctx, kRoleMma)) return;
-        ++q_cnt[i];
+        const int ni = i == 0 ? n0 : n1;
+        if (ni == 0) continue;
+        if (!mbar_wait(&s.q_full[i], (q_phase >> i) & 1u, ctx, kRoleMma)) return;
+        q_phase ^= 1u << i;
         tc_fence_after();
         issue_qk(i, slot_k);
         umma_commit(&s.s_full[i]);
-        if (it.n[i] == 1) umma_commit(&s.q_empty[i]);
+        if (ni == 1) umma_commit(&s.q_empty[i]);
       }
       umma_commit(&s.kv_empty[slot_k]);
 
       for (int j = 0; j < nmax; ++j) {
-        const uint32_t slot_v = kv_cons % NS;
-        if (!mbar_wait(&s.kv_full[slot_v], (kv_cons / NS) & 1, ctx, kRoleMma)) return;
-        ++kv_cons;
+        const uint32_t slot_v = slot;
+        if (!mbar_wait(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
+        advance();
         const bool has_next = (j + 1 < nmax);
         bool k_ready = false;
-        slot_k = kv_cons % NS;
-#pragma unroll
+        slot_k = slot;
+#pragma unroll 1
         for (int i = 0; i < 2; ++i) {
-          if (j < it.n[i]) {
-            if (!mbar_wait(&s.p_full[i], p_cnt[i] & 1, ctx, kRoleMma)) return;
-            ++p_cnt[i];
+          const int ni = i == 0 ? n0 : n1;
+          if (j < ni) {
+            HB_TRACE(p, 12, 10 + i);
+            if (!mbar_wait(&s.p_full[i], (p_phase >> i) & 1u, ctx, kRoleMma)) return;
+            p_phase ^= 1u << i;
             tc_fence_after();
-            issue_pv(i, slot_v, j > 0);
-            if (j == it.n[i] - 1) umma_commit(&s.o_full[i]);
+            HB_TRACE(p, 12, 12 + i);
+            issue_pv(i, slot_v, j > 0 ? 1u : 0u);
+            if (j == ni - 1) umma_commit(&s.o_full[i]);
           }
-          if (j + 1 < it.n[i]) {
+          if (j + 1 < ni) {
             if (!k_ready) {
-              if (!mbar_wait(&s.kv_full[slot_k], (kv_cons / NS) & 1, ctx, kRoleMma)) return;
+              if (!mbar_wait(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
               tc_fence_after();
               k_ready = true;
             }
             issue_qk(i, slot_k);
             umma_commit(&s.s_full[i]);
-            if (j + 2 == it.n[i]) umma_commit(&s.q_empty[i]);
+            HB_TRACE(p, 12, 14 + i);
+            if (j + 2 == ni) umma_commit(&s.q_empty[i]);
           }
         }
         umma_commit(&s.kv_empty[slot_v]);
         if (has_next) {
           umma_commit(&s.kv_empty[slot_k]);
-          ++kv_cons;
+          advance();
         }
       }
     }
@@ -418,7 +464,7 @@ template <typename T, int D, int NS>
 __device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx) {
   constexpr uint32_t kTileBytes = FaSmem<D, NS>::kTileBytes;
   constexpr uint32_t kHalfBytes = kTileM * 128;
-  uint32_t kv_prod = 0, q_cnt[2] = {0, 0};
+  uint32_t slot = 0, phase = 1, q_phase[2] = {1, 1};  // "empty" barriers start out free
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
     for (int half = 0; half < 2; ++half) {
@@ -427,8 +473,8 @@ __device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<D, NS>& s,
       const int nmax = max(it.n[0], it.n[1]);
 
       auto load_q = [&](int i) -> bool {
-        if (!mbar_wait(&s.q_empty[i], (q_cnt[i] & 1) ^ 1, ctx, kRoleTma)) return false;
-        ++q_cnt[i];
+        if (!mbar_wait(&s.q_empty[i], q_phase[i], ctx, kRoleTma)) return false;
+        q_phase[i] ^= 1;
         mbar_arrive_expect_tx(&s.q_full[i], kTileBytes);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
@@ -437,13 +483,15 @@ __device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<D, NS>& s,
         return true;
       };
       auto load_kv = [&](const CUtensorMap* tm, int j) -> bool {
-        const uint32_t slot = kv_prod % NS;
-        if (!mbar_wait(&s.kv_empty[slot], ((kv_prod / NS) & 1) ^ 1, ctx, kRoleTma)) return false;
-        ++kv_prod;
+        if (!mbar_wait(&s.kv_empty[slot], phase, ctx, kRoleTma)) return false;
         mbar_arrive_expect_tx(&s.kv_full[slot], kTileBytes);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
           tma_load_4d(s.kv[slot] + h * kHalfBytes, tm, &s.kv_full[slot], h * 64, j * kTileN, it.hkv, it.b);
+        }
+        if (++slot == NS) {
+          slot = 0;
+          phase ^= 1;
         }
         return true;
       };
@@ -505,13 +553,13 @@ __global__ void __launch_bounds__(kFaThreads, 1) fa_fwd_kernel(const __grid_cons
   const bool run = (s.abort_flag == 0);
 
   if (warp < 8) {
-    reg_inc<192>();
+    reg_inc<184>();
     if (run) fa_softmax_role<T, D, NS>(p, s, ctx, tmem, warp >> 2);
   } else if (warp < 12) {
     reg_dec<80>();
     if (run) fa_correction_role<T, D, NS>(p, s, ctx, tmem);
   } else {
-    reg_dec<48>();
+    reg_dec<64>();
     if (run && lane == 0) {
       if (warp == 12) {
         fa_mma_role<T, D, NS>(p, s, ctx, tmem);

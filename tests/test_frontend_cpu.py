@@ -1,0 +1,214 @@
+"""Graph-level tests of the torch.compile backend: run on a CPU-only host, nothing is executed
+on the kernels (the rewritten graph is inspected, the original one is what runs)."""
+import copy
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import heddle_b200
+from heddle_b200.frontend import backend as B
+from heddle_b200.frontend import fusion, patterns
+
+
+def capture(module, *inputs):
+    """Compile `module` with a recording backend; returns the GraphModule the backend produced."""
+    got = []
+
+    def recording_backend(gm, example_inputs):
+        original = copy.deepcopy(gm)
+        got.append(B.tilelang_backend(gm, example_inputs))
+        return original.forward
+
+    torch._dynamo.reset()
+    with torch.no_grad():
+        torch.compile(module, backend=recording_backend)(*inputs)
+    assert len(got) == 1, "expected a single graph"
+    return got[0]
+
+
+def targets(gm):
+    return [n.target for n in gm.graph.nodes if n.op == "call_function"]
+
+
+def qkv(B_=1, H=2, S=64, D=64, Skv=None, dtype=torch.float32):
+    g = torch.Generator().manual_seed(0)
+    Skv = Skv or S
+    return (torch.randn(B_, H, S, D, generator=g).to(dtype), torch.randn(B_, H, Skv, D, generator=g).to(dtype),
+            torch.randn(B_, H, Skv, D, generator=g).to(dtype))
+
+
+def test_init_is_idempotent_and_names_match_reference():
+    heddle_b200.init()
+    heddle_b200.init()
+    from heddle_b200.frontend import tilelang_backend
+    assert callable(tilelang_backend)
+    for name in ("_tilelang_sdpa_direct", "_tilelang_h2o_attention", "_replace_sdpa_op",
+                 "_replace_expanded_attention", "try_fuse_h2o_attention", "tilelang_backend"):
+        assert hasattr(B, name)
+    for name in ("scaled_dot_product_attention_pattern", "TileLangFlashAttnFunc", "tilelang_flash_attn_wrapper",
+                 "tilelang_flash_attn_replacement", "TileLangH2OFunc", "tilelang_h2o_attention_wrapper",
+                 "_heuristic_config"):
+        assert hasattr(patterns, name)
+    assert patterns._heuristic_config(4, 32, 4096, 4096, 128) == {"block_M": 128, "block_N": 128, "num_stages": 5,
+                                                                  "threads": 512}
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_sdpa_op_is_replaced_with_its_semantics(causal):
+    class M(torch.nn.Module):
+        def forward(self, q, k, v):
+            return F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=0.2)
+
+    gm = capture(M(), *qkv())
+    nodes = [n for n in gm.graph.nodes if n.op == "call_function"]
+    assert [n.target for n in nodes] == [B._tilelang_sdpa_direct]
+    assert nodes[0].kwargs == {"is_causal": causal, "scale": 0.2}
+
+
+def test_sdpa_with_mask_or_dropout_is_left_alone():
+    class M(torch.nn.Module):
+        def forward(self, q, k, v, m):
+            return F.scaled_dot_product_attention(q, k, v, attn_mask=m)
+
+    q, k, v = qkv()
+    gm = capture(M(), q, k, v, torch.zeros(64, 64))
+    assert B._tilelang_sdpa_direct not in targets(gm)
+
+
+def test_expanded_attention_non_causal_config1_module():
+    """The benchmark's first configuration: softmax(Q K^T / sqrt(D)) V, non-causal."""
+    class Attn(torch.nn.Module):
+        def forward(self, q, k, v):
+            s = torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(q.shape[-1])
+            return torch.matmul(torch.softmax(s, dim=-1), v)
+
+    gm = capture(Attn(), *qkv(1, 4, 256, 64))
+    nodes = [n for n in gm.graph.nodes if n.op == "call_function"]
+    assert [n.target for n in nodes] == [B._tilelang_sdpa_direct]
+    assert nodes[0].kwargs["is_causal"] is False
+    assert nodes[0].kwargs["scale"] == pytest.approx(1 / 8)
+
+
+def test_expanded_attention_with_causal_mask_and_past():
+    class Attn(torch.nn.Module):
+        def forward(self, q, k, v):
+            s = torch.matmul(q, k.transpose(-2, -1)) * 0.125
+            Sq, Skv = q.shape[-2], k.shape[-2]
+            s = s + torch.triu(torch.full((Sq, Skv), float("-inf")), diagonal=Skv - Sq + 1)
+            return torch.matmul(torch.softmax(s, dim=-1), v)
+
+    gm = capture(Attn(), *qkv(1, 2, 48, 64, Skv=80))
+    nodes = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is B._tilelang_sdpa_direct]
+    assert len(nodes) == 1 and nodes[0].kwargs == {"is_causal": True, "scale": 0.125}
+    assert not any("softmax" in str(t) for t in targets(gm))
+
+
+def test_expanded_attention_with_other_mask_is_left_alone():
+    class Attn(torch.nn.Module):
+        def forward(self, q, k, v, bias):
+            s = torch.matmul(q, k.transpose(-2, -1)) * 0.125 + bias
+            return torch.matmul(torch.softmax(s, dim=-1), v)
+
+    q, k, v = qkv()
+    gm = capture(Attn(), q, k, v, torch.randn(64, 64))
+    assert B._tilelang_sdpa_direct not in targets(gm)
+    # a mask that is triangular but not the causal one for these lengths
+    class Attn2(torch.nn.Module):
+        def forward(self, q, k, v):
+            s = torch.matmul(q, k.transpose(-2, -1)) * 0.125
+            s = s + torch.triu(torch.full((64, 64), float("-inf")), diagonal=3)
+            return torch.matmul(torch.softmax(s, dim=-1), v)
+
+    assert B._tilelang_sdpa_direct not in targets(capture(Attn2(), q, k, v))
+
+
+def test_bshd_pattern_uses_the_bshd_wrapper():
+    class M(torch.nn.Module):
+        def forward(self, q, k, v):
+            return patterns.scaled_dot_product_attention_pattern(q, k, v, 0.125)
+
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(2, 32, 4, 64, generator=g) for _ in range(3))
+    gm = capture(M(), q, k, v)
+    assert patterns.tilelang_flash_attn_wrapper in targets(gm)
+    assert not any("softmax" in str(t) for t in targets(gm))
+
+
+def test_h2o_structure_is_fused_with_both_outputs():
+    class H2O(torch.nn.Module):
+        def forward(self, q, k, v):
+            s = torch.matmul(q, k.transpose(-2, -1)) / 8.0
+            s = s + torch.triu(torch.full((64, 64), float("-inf")), diagonal=1)
+            p = torch.softmax(s, dim=-1)
+            return torch.matmul(p, v), p.sum(dim=-2)
+
+    gm = capture(H2O(), *qkv())
+    t = targets(gm)
+    assert B._tilelang_h2o_attention in t and B._tilelang_sdpa_direct not in t
+    node = next(n for n in gm.graph.nodes if n.target is B._tilelang_h2o_attention)
+    assert node.kwargs == {"is_causal": True, "scale": pytest.approx(0.125)}
+
+
+def test_env_switch_disables_attention_rewrite(monkeypatch):
+    monkeypatch.setenv("TILELANG_FRONTEND_ENABLE_FLASHATTN_PATTERN", "0")
+    monkeypatch.setenv("TILELANG_FRONTEND_ENABLE_H2O_FUSE", "0")
+
+    class M(torch.nn.Module):
+        def forward(self, q, k, v):
+            return F.scaled_dot_product_attention(q, k, v, is_causal=True)
+
+    assert B._tilelang_sdpa_direct not in targets(capture(M(), *qkv()))
+
+
+def test_direct_leaf_call_keeps_reference_rule_and_rejects_cpu():
+    q, k, v = qkv(dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        B._tilelang_sdpa_direct(q, k, v)
+
+
+# ----------------------------------------------------------------------------------------
+# GEMM + epilogue fusion
+# ----------------------------------------------------------------------------------------
+def test_linear_activation_groups():
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(64, 128, bias=False)
+            self.b = torch.nn.Linear(128, 64, bias=True)
+
+        def forward(self, x):
+            return self.b(F.gelu(self.a(x), approximate="tanh"))
+
+    gm = capture(M().to(torch.bfloat16), torch.randn(4, 16, 64).to(torch.bfloat16))
+    leaves = [n for n in gm.graph.nodes if n.target is fusion.hb_linear]
+    assert [n.kwargs["act"] for n in leaves] == ["gelu_tanh", "none"]
+    assert leaves[1].kwargs["bias"] is not None
+    assert not any("gelu" in str(t) or "linear" == getattr(t, "__name__", "") for t in targets(gm))
+
+
+def test_fp32_linear_is_not_lowered():
+    gm = capture(torch.nn.Linear(64, 64), torch.randn(8, 64))
+    assert fusion.hb_linear not in targets(gm)
+
+
+def test_llama_layer_lowering():
+    from oracle import attention_oracle as O  # the module definition doubles as the test model
+
+    layer = O.LlamaLayer(hidden=256, heads=2, inter=512).init_weights(seed=4).to(torch.bfloat16)
+    x = torch.randn(2, 128, 256).to(torch.bfloat16)
+    gm = capture(layer, x)
+    t = targets(gm)
+    assert t.count(B._tilelang_sdpa_direct) == 1
+    assert t.count(fusion.hb_swiglu) == 1
+    assert t.count(fusion.hb_linear) == 5          # wq, wk, wv, wo, w_down
+    assert t.count(fusion.hb_rms_rowstat) == 2     # one statistic per RMSNorm
+    assert fusion.hb_rmsnorm not in t              # both norms folded into their GEMMs
+    lin = [n for n in gm.graph.nodes if n.target is fusion.hb_linear]
+    assert sum(1 for n in lin if n.kwargs.get("residual") is not None) == 2   # wo and w_down
+    assert sum(1 for n in lin if n.kwargs.get("row_scale") is not None) == 3  # q, k, v projections
+    sw = next(n for n in gm.graph.nodes if n.target is fusion.hb_swiglu)
+    assert sw.kwargs.get("row_scale") is not None and sw.kwargs.get("gamma") is not None
+    sd = next(n for n in gm.graph.nodes if n.target is B._tilelang_sdpa_direct)
+    assert sd.kwargs["is_causal"] is True
