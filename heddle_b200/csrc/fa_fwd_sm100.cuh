@@ -339,7 +339,7 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
 }
 
 // ------------------------------------------------------------------------------------
-// MMA issuer (one thread)
+// MMA issuer (one warp; an elected lane issues)
 // ------------------------------------------------------------------------------------
 template <typename T, int D, int NS>
 __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx,
@@ -358,27 +358,38 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s,
   const uint32_t kv_lo = smem_u32(s.kv[0]) >> 4;
   auto desc = [](uint32_t lo) -> uint64_t { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
 
+  // The whole warp runs this role so that addresses and descriptors stay warp-uniform (they
+  // then live in uniform registers, which is what tcgen05.mma takes); one elected lane issues.
+  const bool leader = elect_one();
+  auto commit = [&](uint64_t* bar) {
+    if (leader) umma_commit(bar);
+  };
+
   auto issue_qk = [&](int i, uint32_t slot) {
     const uint32_t qa = q_lo + static_cast<uint32_t>(i) * kTile16;
     const uint32_t ka = (kv_lo + slot * kTile16) | kLboK;
     const uint32_t d_tmem = tmem + static_cast<uint32_t>(i * kTileN);
+    if (leader) {
 #pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-      // 16 elements (32 bytes) per step inside a 64-element sub-tile, then the next sub-tile
-      constexpr uint32_t kSub = kHalfBytes >> 4;
-      const uint32_t off = static_cast<uint32_t>(kk >> 2) * kSub + static_cast<uint32_t>(kk & 3) * 2u;
-      umma_ss_f16(d_tmem, desc(qa + off), desc(ka + off), idesc_qk, kk > 0 ? 1u : 0u);
+      for (int kk = 0; kk < D / 16; ++kk) {
+        // 16 elements (32 bytes) per step inside a 64-element sub-tile, then the next sub-tile
+        constexpr uint32_t kSub = kHalfBytes >> 4;
+        const uint32_t off = static_cast<uint32_t>(kk >> 2) * kSub + static_cast<uint32_t>(kk & 3) * 2u;
+        umma_ss_f16(d_tmem, desc(qa + off), desc(ka + off), idesc_qk, kk > 0 ? 1u : 0u);
+      }
     }
   };
   auto issue_pv = [&](int i, uint32_t slot, uint32_t accumulate) {
     const uint32_t va = (kv_lo + slot * kTile16) | kLboV;
     const uint32_t d_tmem = tmem + 256u + static_cast<uint32_t>(i * 128);
     const uint32_t a_tmem = tmem + static_cast<uint32_t>(i * kTileN);
+    if (leader) {
 #pragma unroll
-    for (int kk = 0; kk < kTileN / 16; ++kk) {
-      // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2048 bytes) of V
-      umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), desc(va + static_cast<uint32_t>(kk) * 128u), idesc_pv,
-                  kk > 0 ? 1u : accumulate);
+      for (int kk = 0; kk < kTileN / 16; ++kk) {
+        // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2048 bytes) of V
+        umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), desc(va + static_cast<uint32_t>(kk) * 128u),
+                    idesc_pv, kk > 0 ? 1u : accumulate);
+      }
     }
   };
 
@@ -401,24 +412,24 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s,
 
       // step 0 scores
       uint32_t slot_k = slot;
-      if (!mbar_wait(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
+      if (!mbar_wait_warp(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
       advance();
 #pragma unroll 1
       for (int i = 0; i < 2; ++i) {
         const int ni = i == 0 ? n0 : n1;
         if (ni == 0) continue;
-        if (!mbar_wait(&s.q_full[i], (q_phase >> i) & 1u, ctx, kRoleMma)) return;
+        if (!mbar_wait_warp(&s.q_full[i], (q_phase >> i) & 1u, ctx, kRoleMma)) return;
         q_phase ^= 1u << i;
         tc_fence_after();
         issue_qk(i, slot_k);
-        umma_commit(&s.s_full[i]);
-        if (ni == 1) umma_commit(&s.q_empty[i]);
+        commit(&s.s_full[i]);
+        if (ni == 1) commit(&s.q_empty[i]);
       }
-      umma_commit(&s.kv_empty[slot_k]);
+      commit(&s.kv_empty[slot_k]);
 
       for (int j = 0; j < nmax; ++j) {
         const uint32_t slot_v = slot;
-        if (!mbar_wait(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
+        if (!mbar_wait_warp(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
         advance();
         const bool has_next = (j + 1 < nmax);
         bool k_ready = false;
@@ -428,28 +439,28 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s,
           const int ni = i == 0 ? n0 : n1;
           if (j < ni) {
             HB_TRACE(p, 12, 10 + i);
-            if (!mbar_wait(&s.p_full[i], (p_phase >> i) & 1u, ctx, kRoleMma)) return;
+            if (!mbar_wait_warp(&s.p_full[i], (p_phase >> i) & 1u, ctx, kRoleMma)) return;
             p_phase ^= 1u << i;
             tc_fence_after();
             HB_TRACE(p, 12, 12 + i);
             issue_pv(i, slot_v, j > 0 ? 1u : 0u);
-            if (j == ni - 1) umma_commit(&s.o_full[i]);
+            if (j == ni - 1) commit(&s.o_full[i]);
           }
           if (j + 1 < ni) {
             if (!k_ready) {
-              if (!mbar_wait(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
+              if (!mbar_wait_warp(&s.kv_full[slot], phase, ctx, kRoleMma)) return;
               tc_fence_after();
               k_ready = true;
             }
             issue_qk(i, slot_k);
-            umma_commit(&s.s_full[i]);
+            commit(&s.s_full[i]);
             HB_TRACE(p, 12, 14 + i);
-            if (j + 2 == ni) umma_commit(&s.q_empty[i]);
+            if (j + 2 == ni) commit(&s.q_empty[i]);
           }
         }
-        umma_commit(&s.kv_empty[slot_v]);
+        commit(&s.kv_empty[slot_v]);
         if (has_next) {
-          umma_commit(&s.kv_empty[slot_k]);
+          commit(&s.kv_empty[slot_k]);
           advance();
         }
       }
@@ -560,17 +571,16 @@ __global__ void __launch_bounds__(kFaThreads, 1) fa_fwd_kernel(const __grid_cons
     if (run) fa_correction_role<T, D, NS>(p, s, ctx, tmem);
   } else {
     reg_dec<64>();
-    if (run && lane == 0) {
-      if (warp == 12) {
-        fa_mma_role<T, D, NS>(p, s, ctx, tmem);
-        if (s.abort_flag) {
-          // aborting: let the tensor pipe drain before TMEM is released
-          umma_commit(&s.drain);
-          mbar_wait(&s.drain, 0, ctx, kRoleDrain);
-        }
-      } else if (warp == 13) {
-        fa_tma_role<T, D, NS>(p, s, ctx);
+    if (run && warp == 12) {
+      fa_mma_role<T, D, NS>(p, s, ctx, tmem);
+      __syncwarp();
+      if (s.abort_flag && lane == 0) {
+        // aborting: let the tensor pipe drain before TMEM is released
+        umma_commit(&s.drain);
+        mbar_wait(&s.drain, 0, ctx, kRoleDrain);
       }
+    } else if (run && warp == 13 && lane == 0) {
+      fa_tma_role<T, D, NS>(p, s, ctx);
     }
     __syncwarp();
   }

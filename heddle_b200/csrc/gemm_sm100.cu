@@ -163,6 +163,4 @@ int hb_rms_rowstat(const void* x, const void* residual, void* y_out, float* rstd
   return hb::rowstat_impl(x, residual, y_out, rstd, M, N, ldx, eps, dtype, stream);
 }
 
-int hb_h2o_score(const hb_h2o_args*) { return hb::set_error(HB_ERR_UNSUPPORTED, "hb_h2o_score: not built yet"); }
-
 }  // extern "C"

@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     if (run && lane == 0) {
       // ---------------- TMA producer ----------------
       constexpr uint32_t kStageBytes = (kGemmBM + kGemmBN) * kGemmBK * 2;
-      uint32_t it = 0;
+      uint32_t st = 0, phase = 1;  // "empty" barriers start out free
       bool ok = true;
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
         int m_t, n_t;
@@ -308,9 +308,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         const int n0 = n_t * p.tile_cols;
         const int row_b0 = n0;
         const int row_b1 = (EPI == kEpiSwiglu) ? (p.w_row2_offset + n0) : (n0 + 128);
-        for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
-          const uint32_t st = it % kGemmStages;
-          if (!mbar_wait(&s.empty[st], ((it / kGemmStages) & 1) ^ 1, ctx, kGemmRoleTma)) {
+        for (int ks = 0; ks < p.k_steps; ++ks) {
+          if (!mbar_wait(&s.empty[st], phase, ctx, kGemmRoleTma)) {
             ok = false;
             break;
           }
@@ -318,42 +317,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
           tma_load_2d(s.a[st], &p.tm_a, &s.full[st], ks * kGemmBK, m0);
           tma_load_2d(s.b[st], &p.tm_w, &s.full[st], ks * kGemmBK, row_b0);
           tma_load_2d(s.b[st] + 128 * kGemmBK * 2, &p.tm_w, &s.full[st], ks * kGemmBK, row_b1);
+          if (++st == kGemmStages) {
+            st = 0;
+            phase ^= 1;
+          }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (run && lane == 0) {
-      // ---------------- MMA issuer ----------------
+    if (run) {
+      // ---------------- MMA issuer: the whole warp runs the loop (operands stay warp-uniform),
+      // one elected lane issues ----------------
       constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, kGemmBM, kGemmBN, 0, 0);
-      constexpr uint64_t kDesc = (uint64_t(16 >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-      uint32_t it = 0, tile_i = 0;
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kLbo = (16u >> 4) << 16;
+      const bool leader = elect_one();
+      uint32_t stage = 0, phase = 0, tile_i = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++tile_i) {
         const uint32_t acc = tile_i & 1;
-        if (!mbar_wait(&s.acc_empty[acc], ((tile_i >> 1) & 1) ^ 1, ctx, kGemmRoleMma)) {
+        if (!mbar_wait_warp(&s.acc_empty[acc], ((tile_i >> 1) & 1) ^ 1, ctx, kGemmRoleMma)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * kGemmBN;
-        for (int ks = 0; ks < p.k_steps; ++ks, ++it) {
-          const uint32_t st = it % kGemmStages;
-          if (!mbar_wait(&s.full[st], (it / kGemmStages) & 1, ctx, kGemmRoleMma)) {
+        for (int ks = 0; ks < p.k_steps; ++ks) {
+          if (!mbar_wait_warp(&s.full[stage], phase, ctx, kGemmRoleMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a16 = smem_u32(s.a[st]) >> 4, b16 = smem_u32(s.b[st]) >> 4;
+          const uint32_t a_lo = (smem_u32(s.a[stage]) >> 4) | kLbo, b_lo = (smem_u32(s.b[stage]) >> 4) | kLbo;
+          if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < kGemmBK / 16; ++kk) {
-            umma_ss_f16(d_tmem, kDesc | (a16 + kk * 2), kDesc | (b16 + kk * 2), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+              umma_ss_f16(d_tmem, (static_cast<uint64_t>(kDescHi) << 32) | (a_lo + kk * 2),
+                          (static_cast<uint64_t>(kDescHi) << 32) | (b_lo + kk * 2), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(&s.empty[stage]);
           }
-          umma_commit(&s.empty[st]);
+          if (++stage == kGemmStages) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
-        if (ok) umma_commit(&s.acc_full[acc]);
+        if (ok && leader) umma_commit(&s.acc_full[acc]);
       }
-      if (s.abort_flag) {
+      __syncwarp();
+      if (s.abort_flag && lane == 0) {
         umma_commit(&s.drain);
         mbar_wait(&s.drain, 0, ctx, kGemmRoleDrain);
       }

@@ -214,3 +214,33 @@ def rms_rowstat(x: torch.Tensor, residual: Optional[torch.Tensor] = None, eps: f
                                               y.data_ptr() if y is not None else None, rstd.data_ptr(), M, N,
                                               x2.stride(0), float(eps), _DTYPES[x.dtype], _stream_ptr(x.device)))
     return (y.reshape(x.shape) if y is not None else None), rstd.reshape(x.shape[:-1])
+
+
+def h2o_score(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, causal: bool = True,
+              softmax_scale: Optional[float] = None, layout: str = "bhsd") -> torch.Tensor:
+    """H2O score through ``hb_h2o_score``: score[b,h,j] = sum_i exp(s_ij - lse_i), fp32 [B, Hq, Skv].
+
+    ``lse`` is the natural-log LSE [B, Hq, Sq] that ``fa_fwd(..., return_lse=True)`` returns."""
+    _require_cuda(q, k, lse)
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype:
+        raise TypeError(f"unsupported or mismatched dtypes: {q.dtype}, {k.dtype}")
+    q, k = _inner_contiguous(q), _inner_contiguous(k)
+    b_ax, h_ax, s_ax = (0, 1, 2) if layout == "bhsd" else (0, 2, 1)
+    B, Hq, Sq, D = q.shape[b_ax], q.shape[h_ax], q.shape[s_ax], q.shape[3]
+    Hkv, Skv = k.shape[h_ax], k.shape[s_ax]
+    lse = lse.to(torch.float32).contiguous()
+    if tuple(lse.shape) != (B, Hq, Sq):
+        raise ValueError(f"lse must be [B, Hq, Sq] = {(B, Hq, Sq)}, got {tuple(lse.shape)}")
+    score = torch.empty((B, Hq, Skv), dtype=torch.float32, device=q.device)
+    a = _lib.H2oArgs()
+    a.q, a.k, a.lse, a.score = q.data_ptr(), k.data_ptr(), lse.data_ptr(), score.data_ptr()
+    a.B, a.Hq, a.Hkv, a.Sq, a.Skv, a.D = B, Hq, Hkv, Sq, Skv, D
+    a.q_stride_b, a.q_stride_h, a.q_stride_s = q.stride(b_ax), q.stride(h_ax), q.stride(s_ax)
+    a.k_stride_b, a.k_stride_h, a.k_stride_s = k.stride(b_ax), k.stride(h_ax), k.stride(s_ax)
+    a.causal = 1 if causal else 0
+    a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    a.dtype = _DTYPES[q.dtype]
+    a.stream = _stream_ptr(q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().hb_h2o_score(C.byref(a)))
+    return score

@@ -1,0 +1,53 @@
+"""Parity of hb_h2o_score and the H2O attention leaf with the CPU oracle."""
+import pytest
+import torch
+
+from oracle import attention_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(built_lib):
+    from heddle_b200 import ops as _ops
+    return _ops
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,D,causal,dtype", [
+    (1, 2, 2, 128, 128, 128, True, torch.bfloat16),
+    (2, 4, 2, 333, 333, 128, True, torch.bfloat16),
+    (1, 2, 2, 200, 455, 64, True, torch.float16),
+    (1, 3, 3, 300, 300, 128, False, torch.bfloat16),
+    (1, 2, 1, 1024, 1024, 128, True, torch.float16),
+    (1, 1, 1, 77, 900, 64, False, torch.bfloat16),
+])
+def test_h2o_score_matches_oracle(ops, B, Hq, Hkv, Sq, Skv, D, causal, dtype):
+    q, k, v = O.make_qkv(B, Hq, Hkv, Sq, Skv, D, seed=Sq + D, dtype=dtype)
+    out, lse = ops.fa_fwd(q.cuda(), k.cuda(), v.cuda(), causal=causal, return_lse=True)
+    score = ops.h2o_score(q.cuda(), k.cuda(), lse, causal=causal)
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    _, ref_lse = O.attention_eager(q, k, v, causal=causal)
+    ref = O.h2o_score(q, k, ref_lse, causal=causal)
+    assert score.shape == (B, Hq, Skv)
+    # every query row distributes a total probability of 1
+    assert (score.sum(-1).cpu() - Sq).abs().max().item() <= 2e-3 * Sq
+    assert (score.cpu() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_h2o_leaf_and_factories(ops):
+    from heddle_b200.frontend.backend import _tilelang_h2o_attention
+    from heddle_b200.tileop import flashattn_lse, h2o_score
+
+    q, k, v = O.make_qkv(1, 2, 2, 384, 384, 128, seed=3, dtype=torch.float16)
+    out, score = _tilelang_h2o_attention(q.cuda(), k.cuda(), v.cuda())
+    ref_out, ref_lse = O.attention_eager(q, k, v, causal=True)
+    assert (out.cpu().float() - ref_out).abs().max().item() <= 2e-2
+    ref = O.h2o_score(q, k, ref_lse, causal=True)
+    assert (score.cpu() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    # the reference's factory protocol: (LSE log2-domain [B,H,S,1], O), then h2o_score(Q, K, LSE)
+    lse2, o2 = flashattn_lse(1, 2, 384, 384, 128, True)(q.cuda(), k.cuda(), v.cuda())
+    assert lse2.shape == (1, 2, 384, 1)
+    assert (lse2[..., 0].cpu() - ref_lse * O.LOG2E).abs().max().item() <= 2e-3
+    s2 = h2o_score(1, 2, 384, 384, 128, True)(q.cuda(), k.cuda(), lse2)
+    assert torch.allclose(s2, score, rtol=1e-4, atol=1e-4)
