@@ -36,18 +36,16 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units; below it the stale max
 // Optional phase tracing (compiled in with -DHB_FA_TRACE only): lane 0 of selected warps of
 // CTA 0 appends (clock64 << 8 | code) records to a caller-provided buffer, 4096 slots per region.
 #ifdef HB_FA_TRACE
-#define HB_TRACE(p, region, code)                                                          \
-  do {                                                                                     \
-    if ((p).trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {              \
-      unsigned long long* t_ = (p).trace + (region) * 4096;                                \
-      const unsigned long long n_ = t_[0];                                                 \
-      if (n_ < 4094) {                                                                     \
-        t_[1 + n_] = (static_cast<unsigned long long>(clock64()) << 8) | (code);           \
-        t_[0] = n_ + 1;                                                                    \
-      }                                                                                    \
-    }                                                                                      \
+#define HB_TRACE_DECL uint32_t hb_trace_n = 0;
+#define HB_TRACE(p, region, code)                                                                        \
+  do {                                                                                                   \
+    if ((p).trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && hb_trace_n < 4094) {       \
+      (p).trace[(region) * 4096 + 1 + hb_trace_n] = (static_cast<unsigned long long>(clock64()) << 8) | (code); \
+      (p).trace[(region) * 4096] = ++hb_trace_n;                                                         \
+    }                                                                                                    \
   } while (0)
 #else
+#define HB_TRACE_DECL
 #define HB_TRACE(p, region, code) \
   do {                            \
   } while (0)
@@ -135,6 +133,7 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
   const uint32_t tS = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(i * kTileN);
   const float scale_log2 = p.scale_log2;
   uint32_t s_cnt = 0, c_cnt = 0;
+  HB_TRACE_DECL
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
     for (int half = 0; half < 2; ++half) {
@@ -171,12 +170,14 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
         float mx0 = __uint_as_float(v[0]), mx1 = __uint_as_float(v[1]);
         float mx2 = __uint_as_float(v[2]), mx3 = __uint_as_float(v[3]);
 #pragma unroll
-        for (int c = 4; c < kTileN; c += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(v[c]));
-          mx1 = fmaxf(mx1, __uint_as_float(v[c + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(v[c + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(v[c + 3]));
+        for (int c = 4; c < kTileN - 4; c += 8) {
+          mx0 = max3(mx0, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+          mx1 = max3(mx1, __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+          mx2 = max3(mx2, __uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
+          mx3 = max3(mx3, __uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
         }
+        mx0 = max3(mx0, __uint_as_float(v[kTileN - 4]), __uint_as_float(v[kTileN - 3]));
+        mx1 = max3(mx1, __uint_as_float(v[kTileN - 2]), __uint_as_float(v[kTileN - 1]));
         const float row_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 
         // New running max; a max that moved by less than the threshold is not adopted,
@@ -209,10 +210,11 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
 #pragma unroll
           for (int e = 0; e < 32; e += 4) {
             const int c = q * 32 + e;
+            // three of four exponentials on the MUFU, the fourth on the FMA/ALU pipes
             const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), scale_log2, -m_scaled));
             const float p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), scale_log2, -m_scaled));
             const float p2 = fast_exp2(fmaf(__uint_as_float(v[c + 2]), scale_log2, -m_scaled));
-            const float p3 = fast_exp2(fmaf(__uint_as_float(v[c + 3]), scale_log2, -m_scaled));
+            const float p3 = exp2_poly(fmaf(__uint_as_float(v[c + 3]), scale_log2, -m_scaled));
             sum0 += p0;
             sum1 += p1;
             sum2 += p2;
@@ -253,6 +255,7 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
   const int row = threadIdx.x & (kTileM - 1);
   const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
   uint32_t c_cnt[2] = {0, 0}, o_cnt[2] = {0, 0};
+  HB_TRACE_DECL
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
     for (int half = 0; half < 2; ++half) {
@@ -402,6 +405,7 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s,
     }
   };
   uint32_t q_phase = 0, p_phase = 0;  // bit i = parity of tile i's barrier
+  HB_TRACE_DECL
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
     for (int half = 0; half < 2; ++half) {

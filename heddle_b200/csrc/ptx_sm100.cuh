@@ -55,6 +55,28 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// 2^x on the FMA/ALU pipes instead of the MUFU: round-to-nearest split x = n + f with
+// f in [-0.5, 0.5], a cubic for 2^f (relative error 7.5e-5, far below the 16-bit rounding
+// the result gets), n added into the exponent field.  Valid for x <= ~100; x below -126
+// (including -inf) returns 2^-126.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float magic = 12582912.0f;  // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float xf = x + magic;
+  const float fr = x - (xf - magic);
+  float p = fmaf(fr, 0.0551716685f, 0.2426111251f);
+  p = fmaf(p, fr, 0.6932609677f);
+  p = fmaf(p, fr, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xf) << 23));
+}
+
 __device__ __forceinline__ float fast_log2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
