@@ -84,7 +84,6 @@ struct FaSmem {
   uint64_t s_full[2];     // MMA -> softmax: S_i holds the scores of the next step
   uint64_t p_full[2];     // softmax + correction -> MMA: P_i written and O_i rescaled
   uint64_t corr_full[2];  // softmax -> correction: alpha (or final l, m) published
-  uint64_t corr_empty[2];
   uint64_t o_full[2];     // MMA -> correction: O_i complete
   uint64_t drain;
   uint32_t tmem_base;
@@ -132,7 +131,7 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
   const int row = threadIdx.x & (kTileM - 1);
   const uint32_t tS = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(i * kTileN);
   const float scale_log2 = p.scale_log2;
-  uint32_t s_cnt = 0, c_cnt = 0;
+  uint32_t s_cnt = 0, p_cnt = 0;  // completed s_full waits / own p_full arrivals
   HB_TRACE_DECL
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
@@ -182,25 +181,25 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
 
         // New running max; a max that moved by less than the threshold is not adopted,
         // so O needs no rescale for it (l and O stay relative to the same stale max).
-        float m_new = fmaxf(m, row_max);
-        float alpha = 1.f;
-        if (m_new != -INFINITY) {
-          const float diff = (m - m_new) * scale_log2;
-          if (diff >= -kRescaleThreshold) {
-            m_new = m;
-          } else {
-            alpha = fast_exp2(diff);
-          }
-        }
-        m = m_new;
+        // Branch-free: m = -inf (first step) gives diff = -inf -> adopt, alpha = 0;
+        // m_cand = -inf (nothing visible yet) gives NaN comparisons -> keep, alpha = 1.
+        const float m_cand = fmaxf(m, row_max);
+        const float diff = (m - m_cand) * scale_log2;
+        const bool adopt = diff < -kRescaleThreshold;
+        const float alpha = adopt ? fast_exp2(diff) : 1.f;
+        m = adopt ? m_cand : m;
         const float m_scaled = (m == -INFINITY) ? 0.f : m * scale_log2;
 
-        // publish alpha for the correction warpgroup as early as possible
-        if (!mbar_wait_warp(&s.corr_empty[i], (c_cnt & 1) ^ 1, ctx, kRoleSoftmax)) return;
-        s.alpha[i][row] = alpha;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.corr_full[i]);
-        ++c_cnt;
+        // Publish alpha for the correction warpgroup as early as possible.  The slot is free by
+        // construction: S(j) only exists because PV(j-1) was issued, which needed the correction
+        // warpgroup's arrival for step j-1, which it makes after reading alpha(j-1).  Step 0 has
+        // no O to rescale: nothing is written or signalled (the slot may still hold the previous
+        // block's row sum, which the correction warpgroup reads in its epilogue).
+        if (j > 0) {
+          s.alpha[i][row] = alpha;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.corr_full[i]);
+        }
         HB_TRACE(p, warp, 3);
 
         float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
@@ -208,19 +207,18 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
         for (int q = 0; q < kTileN / 32; ++q) {
           uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            const int c = q * 32 + e;
-            // three of four exponentials on the MUFU, the fourth on the FMA/ALU pipes
-            const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), scale_log2, -m_scaled));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), scale_log2, -m_scaled));
-            const float p2 = fast_exp2(fmaf(__uint_as_float(v[c + 2]), scale_log2, -m_scaled));
-            const float p3 = exp2_poly(fmaf(__uint_as_float(v[c + 3]), scale_log2, -m_scaled));
-            sum0 += p0;
-            sum1 += p1;
-            sum2 += p2;
-            sum3 += p3;
-            pk[e / 2] = Pack2<T>::pack(p0, p1);
-            pk[e / 2 + 1] = Pack2<T>::pack(p2, p3);
+          for (int e = 0; e < 32; e += 8) {
+            float pe[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) pe[u] = fmaf(__uint_as_float(v[q * 32 + e + u]), scale_log2, -m_scaled);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) pe[u] = fast_exp2(pe[u]);
+            sum0 += pe[0] + pe[4];
+            sum1 += pe[1] + pe[5];
+            sum2 += pe[2] + pe[6];
+            sum3 += pe[3] + pe[7];
+#pragma unroll
+            for (int u = 0; u < 8; u += 2) pk[(e + u) / 2] = Pack2<T>::pack(pe[u], pe[u + 1]);
           }
           tmem_st16(tS + q * 16, pk);
         }
@@ -231,16 +229,18 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.p_full[i]);
+        ++p_cnt;
         HB_TRACE(p, warp, 5);
       }
 
-      // final row statistics for the epilogue
-      if (!mbar_wait_warp(&s.corr_empty[i], (c_cnt & 1) ^ 1, ctx, kRoleSoftmax)) return;
+      // Final row statistics for the epilogue, in the alpha slot.  The last alpha must have been
+      // consumed first: the correction warpgroup arrives on p_full after reading it (and, for a
+      // one-step block, after the previous block's epilogue read this slot).
+      if (!mbar_wait_warp(&s.p_full[i], (p_cnt & 1) ^ 1, ctx, kRoleSoftmax)) return;
       s.alpha[i][row] = l;
       s.stat_m[i][row] = m;
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.corr_full[i]);
-      ++c_cnt;
     }
   }
 }
@@ -267,12 +267,13 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           if (j >= it.n[i]) continue;
-          if (!mbar_wait_warp(&s.corr_full[i], c_cnt[i] & 1, ctx, kRoleCorrection)) return;
-          ++c_cnt[i];
+          float a = 1.f;
+          if (j > 0) {
+            if (!mbar_wait_warp(&s.corr_full[i], c_cnt[i] & 1, ctx, kRoleCorrection)) return;
+            ++c_cnt[i];
+            a = s.alpha[i][row];
+          }
           HB_TRACE(p, warp, 20 + i);
-          const float a = s.alpha[i][row];
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&s.corr_empty[i]);
           if (j > 0 && __any_sync(0xffffffffu, a != 1.f)) {
             tc_fence_after();
             const uint32_t tO = tmem + lane_off + 256u + static_cast<uint32_t>(i * 128);
@@ -302,8 +303,6 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
         ++c_cnt[i];
         const float l = s.alpha[i][row];
         const float m = s.stat_m[i][row];
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.corr_empty[i]);
         if (!mbar_wait_warp(&s.o_full[i], o_cnt[i] & 1, ctx, kRoleCorrection)) return;
         ++o_cnt[i];
         tc_fence_after();
@@ -541,7 +540,6 @@ __global__ void __launch_bounds__(kFaThreads, 1) fa_fwd_kernel(const __grid_cons
       mbar_init(&s.s_full[i], 1);
       mbar_init(&s.p_full[i], 8);
       mbar_init(&s.corr_full[i], 4);
-      mbar_init(&s.corr_empty[i], 4);
       mbar_init(&s.o_full[i], 1);
     }
     for (int i = 0; i < NS; ++i) {
