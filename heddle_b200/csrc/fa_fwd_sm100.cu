@@ -9,21 +9,16 @@
 
 namespace hb {
 
-template <int D>
-struct FaConfig;
-template <>
-struct FaConfig<128> {
-  static constexpr int kStages = 5;
-};
-template <>
-struct FaConfig<64> {
-  static constexpr int kStages = 8;
+// K/V ring depth: as many 128-key tiles as fit next to the two Q tiles in 227 KB.
+template <typename T, int D>
+struct FaConfig {
+  static constexpr int kStages = (D == 128 && FaTraits<T>::kElemBytes == 2) ? 5 : 8;
 };
 
 template <typename T, int D>
 static int launch_fa(const FaParams& p, int grid, int smem_optin, cudaStream_t stream) {
-  constexpr int NS = FaConfig<D>::kStages;
-  using Smem = FaSmem<D, NS>;
+  constexpr int NS = FaConfig<T, D>::kStages;
+  using Smem = FaSmem<T, D, NS>;
   if ((int)sizeof(Smem) > smem_optin)
     return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: kernel needs %d bytes of shared memory, device offers %d",
                      (int)sizeof(Smem), smem_optin);
@@ -53,9 +48,10 @@ static int fa_fwd_impl(const hb_fa_args* a) {
     return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
   if (a->dtype != HB_BF16 && a->dtype != HB_FP16 && a->dtype != HB_FP8_E4M3)
     return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: unknown dtype %d", a->dtype);
-  if (a->dtype == HB_FP8_E4M3) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: FP8 path not built yet");
   if (a->D != 64 && a->D != 128)
     return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: head_dim %d not supported (64 or 128)", a->D);
+  if (a->dtype == HB_FP8_E4M3 && a->D != 128)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: FP8 needs head_dim 128 (got %d)", a->D);
   if (a->B == 0 || a->Sq == 0) return HB_OK;  // nothing to compute
   if (a->Skv == 0) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: Skv is 0 (softmax over an empty set)");
   if (a->causal && a->Skv < a->Sq)
@@ -64,8 +60,9 @@ static int fa_fwd_impl(const hb_fa_args* a) {
   if (a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr)
     return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: q, k, v and o must be non-NULL");
   const size_t es = dtype_size(a->dtype);
-  if ((reinterpret_cast<uintptr_t>(a->o) & 15u) != 0 || ((a->o_stride_s * es) & 15u) != 0 ||
-      ((a->o_stride_h * es) & 15u) != 0 || ((a->o_stride_b * es) & 15u) != 0)
+  const size_t eso = 2;  // O is 16-bit for every input dtype
+  if ((reinterpret_cast<uintptr_t>(a->o) & 15u) != 0 || ((a->o_stride_s * eso) & 15u) != 0 ||
+      ((a->o_stride_h * eso) & 15u) != 0 || ((a->o_stride_b * eso) & 15u) != 0)
     return set_error(HB_ERR_ALIGN, "hb_fa_fwd: o and its strides must be 16-byte aligned");
   if (a->lse != nullptr && (reinterpret_cast<uintptr_t>(a->lse) & 3u) != 0)
     return set_error(HB_ERR_ALIGN, "hb_fa_fwd: lse must be 4-byte aligned");
@@ -76,9 +73,10 @@ static int fa_fwd_impl(const hb_fa_args* a) {
 
   FaParams p;
   memset(&p, 0, sizeof(p));
-  const CUtensorMapDataType dt =
-      a->dtype == HB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const uint32_t box[4] = {64, (uint32_t)kTileM, 1, 1};
+  const CUtensorMapDataType dt = a->dtype == HB_BF16   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : a->dtype == HB_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const uint32_t box[4] = {(uint32_t)(128 / es), (uint32_t)kTileM, 1, 1};  // 128 bytes of head_dim x 128 rows
   {
     const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Sq, (uint64_t)a->Hq, (uint64_t)a->B};
     const uint64_t str[3] = {(uint64_t)a->q_stride_s * es, (uint64_t)a->q_stride_h * es, (uint64_t)a->q_stride_b * es};
@@ -121,11 +119,25 @@ static int fa_fwd_impl(const hb_fa_args* a) {
   p.nkv = (a->Skv + kTileN - 1) / kTileN;
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->D);
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.out_scale = 1.0f;
+  if (a->dtype == HB_FP8_E4M3) {
+    // scores of the quantised operands are q_scale * k_scale too small; P carries the kernel's
+    // fixed requantisation factor, V its dequantisation scale
+    const float qs = a->q_scale > 0.f ? a->q_scale : 1.0f, ks = a->k_scale > 0.f ? a->k_scale : 1.0f;
+    const float vs = a->v_scale > 0.f ? a->v_scale : 1.0f, os = a->o_scale > 0.f ? a->o_scale : 1.0f;
+    if (a->p_scale > 0.f && a->p_scale != 1.0f / FaTraits<__nv_fp8_e4m3>::kPScale)
+      return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: p_scale is fixed at 1/%d in this build (pass 0)",
+                       (int)FaTraits<__nv_fp8_e4m3>::kPScale);
+    p.scale_log2 *= qs * ks;
+    p.out_scale = vs / (FaTraits<__nv_fp8_e4m3>::kPScale * os);
+  }
 
   const int grid = (int)std::min<long long>(total, st->sm_count);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (a->dtype == HB_FP8_E4M3) return launch_fa<__nv_fp8_e4m3, 128>(p, grid, st->smem_optin, stream);
   if (a->dtype == HB_BF16) {
-    return a->D == 128 ? launch_fa<__nv_bfloat16, 128>(p, grid, st->smem_optin, stream) : launch_fa<__nv_bfloat16, 64>(p, grid, st->smem_optin, stream);
+    return a->D == 128 ? launch_fa<__nv_bfloat16, 128>(p, grid, st->smem_optin, stream)
+                       : launch_fa<__nv_bfloat16, 64>(p, grid, st->smem_optin, stream);
   }
   return a->D == 128 ? launch_fa<__half, 128>(p, grid, st->smem_optin, stream) : launch_fa<__half, 64>(p, grid, st->smem_optin, stream);
 }
@@ -241,6 +253,7 @@ static int fa_fwd_noalloc_impl(const hb_fa_args* a) {
   p.nkv = (a->Skv + kTileN - 1) / kTileN;
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->D);
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.out_scale = 1.0f;
   const int grid = (int)std::min<long long>(total, info.sm_count);
   if (a->dtype == HB_BF16) {
     return a->D == 128 ? launch_fa<__nv_bfloat16, 128>(p, grid, info.smem_optin, stream)
@@ -396,7 +409,7 @@ static int debug_umma_impl(int mode, const void* a, const void* b, float* out, i
   return HB_OK;
 }
 
-int fa_smem_bytes() { return (int)sizeof(FaSmem<128, FaConfig<128>::kStages>); }
+int fa_smem_bytes() { return (int)sizeof(FaSmem<__nv_bfloat16, 128, FaConfig<__nv_bfloat16, 128>::kStages>); }
 
 }  // namespace hb
 

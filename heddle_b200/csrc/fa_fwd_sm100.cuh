@@ -31,7 +31,29 @@ namespace hb {
 constexpr int kFaThreads = 512;
 constexpr int kTileM = 128;  // query rows per softmax warpgroup
 constexpr int kTileN = 128;  // keys per step
-constexpr float kRescaleThreshold = 8.0f;  // log2 units; below it the stale max is kept
+
+// Per-dtype constants.  16-bit inputs: P is written in the input dtype; a running max that
+// grew by less than 2^8 is not adopted.  FP8 e4m3 inputs: P is requantised to e4m3 as
+// p * 32 (the factor is divided out in the epilogue) and the adoption threshold is 2^3, so
+// that the largest P value, 8 * 32 = 256, stays below the e4m3 maximum of 448; O is bf16.
+template <typename T>
+struct FaTraits {
+  using Out = T;
+  static constexpr int kElemBytes = 2;
+  static constexpr bool kFp8 = false;
+  static constexpr uint32_t kFormat = Pack2<T>::kFormat;
+  static constexpr float kRescaleThreshold = 8.0f;  // log2 units
+  static constexpr float kPScale = 1.0f;
+};
+template <>
+struct FaTraits<__nv_fp8_e4m3> {
+  using Out = __nv_bfloat16;
+  static constexpr int kElemBytes = 1;
+  static constexpr bool kFp8 = true;
+  static constexpr uint32_t kFormat = 0;  // e4m3 in kind::f8f6f4
+  static constexpr float kRescaleThreshold = 3.0f;
+  static constexpr float kPScale = 32.0f;
+};
 
 // Optional phase tracing (compiled in with -DHB_FA_TRACE only): lane 0 of selected warps of
 // CTA 0 appends (clock64 << 8 | code) records to a caller-provided buffer, 4096 slots per region.
@@ -69,12 +91,13 @@ struct alignas(64) FaParams {
   int npairs;       // ceil(nqb / 2)
   int total_pairs;  // B * Hq * npairs
   int nkv;          // 128-key tiles
-  float scale_log2; // softmax_scale * log2(e)
+  float scale_log2; // softmax_scale * log2(e) (times q_scale * k_scale for FP8)
+  float out_scale;  // multiplies O / l in the epilogue (v_scale / P scale for FP8, else 1)
 };
 
-template <int D, int NS>
+template <typename T, int D, int NS>
 struct FaSmem {
-  static constexpr int kTileBytes = kTileM * D * 2;
+  static constexpr int kTileBytes = kTileM * D * FaTraits<T>::kElemBytes;
   alignas(1024) uint8_t q[2][kTileBytes];
   alignas(1024) uint8_t kv[NS][kTileBytes];
   float alpha[2][kTileM];   // per-step rescale factor; carries the final row sum at the end of a block
@@ -125,7 +148,7 @@ __device__ __forceinline__ bool fa_get_item(const FaParams& p, int g, int half, 
 // softmax warpgroup (tile i): one query row per thread
 // ------------------------------------------------------------------------------------
 template <typename T, int D, int NS>
-__device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx,
+__device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<T, D, NS>& s, const AbortCtx& ctx,
                                                 uint32_t tmem, int i) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = threadIdx.x & (kTileM - 1);
@@ -185,7 +208,7 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
         // m_cand = -inf (nothing visible yet) gives NaN comparisons -> keep, alpha = 1.
         const float m_cand = fmaxf(m, row_max);
         const float diff = (m - m_cand) * scale_log2;
-        const bool adopt = diff < -kRescaleThreshold;
+        const bool adopt = diff < -FaTraits<T>::kRescaleThreshold;
         const float alpha = adopt ? fast_exp2(diff) : 1.f;
         m = adopt ? m_cand : m;
         const float m_scaled = (m == -INFINITY) ? 0.f : m * scale_log2;
@@ -203,24 +226,48 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
         HB_TRACE(p, warp, 3);
 
         float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        if constexpr (!FaTraits<T>::kFp8) {
 #pragma unroll
-        for (int q = 0; q < kTileN / 32; ++q) {
-          uint32_t pk[16];
+          for (int q = 0; q < kTileN / 32; ++q) {
+            uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            float pe[8];
+            for (int e = 0; e < 32; e += 8) {
+              float pe[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) pe[u] = fmaf(__uint_as_float(v[q * 32 + e + u]), scale_log2, -m_scaled);
+              for (int u = 0; u < 8; ++u) pe[u] = fmaf(__uint_as_float(v[q * 32 + e + u]), scale_log2, -m_scaled);
 #pragma unroll
-            for (int u = 0; u < 8; ++u) pe[u] = fast_exp2(pe[u]);
-            sum0 += pe[0] + pe[4];
-            sum1 += pe[1] + pe[5];
-            sum2 += pe[2] + pe[6];
-            sum3 += pe[3] + pe[7];
+              for (int u = 0; u < 8; ++u) pe[u] = fast_exp2(pe[u]);
+              sum0 += pe[0] + pe[4];
+              sum1 += pe[1] + pe[5];
+              sum2 += pe[2] + pe[6];
+              sum3 += pe[3] + pe[7];
 #pragma unroll
-            for (int u = 0; u < 8; u += 2) pk[(e + u) / 2] = Pack2<T>::pack(pe[u], pe[u + 1]);
+              for (int u = 0; u < 8; u += 2) pk[(e + u) / 2] = Pack2<T>::pack(pe[u], pe[u + 1]);
+            }
+            tmem_st16(tS + q * 16, pk);
           }
-          tmem_st16(tS + q * 16, pk);
+        } else {
+          // e4m3 P: four values per TMEM column, scaled by kPScale (a power of two, exact)
+#pragma unroll
+          for (int q = 0; q < kTileN / 64; ++q) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 64; e += 8) {
+              float pe[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) pe[u] = fmaf(__uint_as_float(v[q * 64 + e + u]), scale_log2, -m_scaled);
+#pragma unroll
+              for (int u = 0; u < 8; ++u) pe[u] = fast_exp2(pe[u]);
+              sum0 += pe[0] + pe[4];
+              sum1 += pe[1] + pe[5];
+              sum2 += pe[2] + pe[6];
+              sum3 += pe[3] + pe[7];
+              constexpr float ps = FaTraits<T>::kPScale;
+              pk[e / 4] = pack4_e4m3(pe[0] * ps, pe[1] * ps, pe[2] * ps, pe[3] * ps);
+              pk[e / 4 + 1] = pack4_e4m3(pe[4] * ps, pe[5] * ps, pe[6] * ps, pe[7] * ps);
+            }
+            tmem_st16(tS + q * 16, pk);
+          }
         }
         l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
         HB_TRACE(p, warp, 4);
@@ -249,7 +296,7 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<D, NS>
 // correction warpgroup
 // ------------------------------------------------------------------------------------
 template <typename T, int D, int NS>
-__device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx,
+__device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<T, D, NS>& s, const AbortCtx& ctx,
                                                    uint32_t tmem) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = threadIdx.x & (kTileM - 1);
@@ -309,8 +356,9 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
 
         const int qrow = it.q0 + kTileM * i + row;
         const bool live = qrow < p.Sq;
-        const float inv_l = (l > 0.f) ? (1.f / l) : 0.f;
-        T* orow = static_cast<T*>(p.o) + it.b * p.o_sb + it.hq * p.o_sh + static_cast<long long>(qrow) * p.o_ss;
+        using Out = typename FaTraits<T>::Out;
+        const float inv_l = (l > 0.f) ? (p.out_scale / l) : 0.f;
+        Out* orow = static_cast<Out*>(p.o) + it.b * p.o_sb + it.hq * p.o_sh + static_cast<long long>(qrow) * p.o_ss;
         const uint32_t tO = tmem + lane_off + 256u + static_cast<uint32_t>(i * 128);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -322,10 +370,10 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               uint4 w;
-              w.x = Pack2<T>::pack(__uint_as_float(r[e]) * inv_l, __uint_as_float(r[e + 1]) * inv_l);
-              w.y = Pack2<T>::pack(__uint_as_float(r[e + 2]) * inv_l, __uint_as_float(r[e + 3]) * inv_l);
-              w.z = Pack2<T>::pack(__uint_as_float(r[e + 4]) * inv_l, __uint_as_float(r[e + 5]) * inv_l);
-              w.w = Pack2<T>::pack(__uint_as_float(r[e + 6]) * inv_l, __uint_as_float(r[e + 7]) * inv_l);
+              w.x = Pack2<Out>::pack(__uint_as_float(r[e]) * inv_l, __uint_as_float(r[e + 1]) * inv_l);
+              w.y = Pack2<Out>::pack(__uint_as_float(r[e + 2]) * inv_l, __uint_as_float(r[e + 3]) * inv_l);
+              w.z = Pack2<Out>::pack(__uint_as_float(r[e + 4]) * inv_l, __uint_as_float(r[e + 5]) * inv_l);
+              w.w = Pack2<Out>::pack(__uint_as_float(r[e + 6]) * inv_l, __uint_as_float(r[e + 7]) * inv_l);
               *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
             }
           }
@@ -344,18 +392,22 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<D, 
 // MMA issuer (one warp; an elected lane issues)
 // ------------------------------------------------------------------------------------
 template <typename T, int D, int NS>
-__device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx,
+__device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<T, D, NS>& s, const AbortCtx& ctx,
                                             uint32_t tmem) {
-  constexpr uint32_t kFmt = Pack2<T>::kFormat;
+  using Tr = FaTraits<T>;
+  constexpr uint32_t kFmt = Tr::kFormat;
   constexpr uint32_t idesc_qk = make_idesc(kFmt, kTileM, kTileN, 0, 0);
   constexpr uint32_t idesc_pv = make_idesc(kFmt, kTileM, D, 0, 1);
-  constexpr uint32_t kHalfBytes = kTileM * 128;  // one 64-element-wide, 128-row sub-tile
+  constexpr uint32_t kSubBytes = kTileM * 128;            // one 128-byte-wide, 128-row sub-tile
+  constexpr int kQkSteps = D * Tr::kElemBytes / 32;       // each MMA consumes 32 bytes of head_dim
+  constexpr int kPvSteps = kTileN * Tr::kElemBytes / 32;  // ... and 32 bytes' worth of keys of P
+  constexpr uint32_t kVStep16 = (32u / Tr::kElemBytes) * 128u >> 4;  // V rows per MMA x 128 B, in 16-byte units
   // Shared-memory descriptors: the high word (SBO = 1024 B, version 1, SWIZZLE_128B) is constant;
   // the low word is (address >> 4) | (LBO >> 4) << 16 and only its address field moves per MMA.
   constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
   constexpr uint32_t kLboK = (16u >> 4) << 16;
-  constexpr uint32_t kLboV = (kHalfBytes >> 4) << 16;
-  constexpr uint32_t kTile16 = FaSmem<D, NS>::kTileBytes >> 4;
+  constexpr uint32_t kLboV = (kSubBytes >> 4) << 16;  // next 128-byte group of head_dim
+  constexpr uint32_t kTile16 = FaSmem<T, D, NS>::kTileBytes >> 4;
   const uint32_t q_lo = (smem_u32(s.q[0]) >> 4) | kLboK;
   const uint32_t kv_lo = smem_u32(s.kv[0]) >> 4;
   auto desc = [](uint32_t lo) -> uint64_t { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
@@ -373,11 +425,15 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s,
     const uint32_t d_tmem = tmem + static_cast<uint32_t>(i * kTileN);
     if (leader) {
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        // 16 elements (32 bytes) per step inside a 64-element sub-tile, then the next sub-tile
-        constexpr uint32_t kSub = kHalfBytes >> 4;
+      for (int kk = 0; kk < kQkSteps; ++kk) {
+        // 32 bytes per step inside a 128-byte-wide sub-tile, then the next sub-tile
+        constexpr uint32_t kSub = kSubBytes >> 4;
         const uint32_t off = static_cast<uint32_t>(kk >> 2) * kSub + static_cast<uint32_t>(kk & 3) * 2u;
-        umma_ss_f16(d_tmem, desc(qa + off), desc(ka + off), idesc_qk, kk > 0 ? 1u : 0u);
+        if constexpr (Tr::kFp8) {
+          umma_ss_f8(d_tmem, desc(qa + off), desc(ka + off), idesc_qk, kk > 0 ? 1u : 0u);
+        } else {
+          umma_ss_f16(d_tmem, desc(qa + off), desc(ka + off), idesc_qk, kk > 0 ? 1u : 0u);
+        }
       }
     }
   };
@@ -387,10 +443,15 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s,
     const uint32_t a_tmem = tmem + static_cast<uint32_t>(i * kTileN);
     if (leader) {
 #pragma unroll
-      for (int kk = 0; kk < kTileN / 16; ++kk) {
-        // 16 keys per step: 8 TMEM columns of packed P, 16 rows (2048 bytes) of V
-        umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), desc(va + static_cast<uint32_t>(kk) * 128u),
-                    idesc_pv, kk > 0 ? 1u : accumulate);
+      for (int kk = 0; kk < kPvSteps; ++kk) {
+        // per step: 8 TMEM columns of packed P, and the matching key rows of V
+        if constexpr (Tr::kFp8) {
+          umma_ts_f8(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), desc(va + static_cast<uint32_t>(kk) * kVStep16),
+                     idesc_pv, kk > 0 ? 1u : accumulate);
+        } else {
+          umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), desc(va + static_cast<uint32_t>(kk) * kVStep16),
+                      idesc_pv, kk > 0 ? 1u : accumulate);
+        }
       }
     }
   };
@@ -475,9 +536,11 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<D, NS>& s,
 // TMA producer (one thread)
 // ------------------------------------------------------------------------------------
 template <typename T, int D, int NS>
-__device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<D, NS>& s, const AbortCtx& ctx) {
-  constexpr uint32_t kTileBytes = FaSmem<D, NS>::kTileBytes;
-  constexpr uint32_t kHalfBytes = kTileM * 128;
+__device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<T, D, NS>& s, const AbortCtx& ctx) {
+  constexpr uint32_t kTileBytes = FaSmem<T, D, NS>::kTileBytes;
+  constexpr uint32_t kSubBytes = kTileM * 128;                       // 128-byte-wide, 128-row sub-tile
+  constexpr int kSubTiles = D * FaTraits<T>::kElemBytes / 128;      // sub-tiles per tile
+  constexpr int kSubElems = 128 / FaTraits<T>::kElemBytes;          // head_dim elements per sub-tile
   uint32_t slot = 0, phase = 1, q_phase[2] = {1, 1};  // "empty" barriers start out free
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
@@ -491,8 +554,8 @@ __device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<D, NS>& s,
         q_phase[i] ^= 1;
         mbar_arrive_expect_tx(&s.q_full[i], kTileBytes);
 #pragma unroll
-        for (int h = 0; h < D / 64; ++h) {
-          tma_load_4d(s.q[i] + h * kHalfBytes, &p.tm_q, &s.q_full[i], h * 64, it.q0 + kTileM * i, it.hq, it.b);
+        for (int h = 0; h < kSubTiles; ++h) {
+          tma_load_4d(s.q[i] + h * kSubBytes, &p.tm_q, &s.q_full[i], h * kSubElems, it.q0 + kTileM * i, it.hq, it.b);
         }
         return true;
       };
@@ -500,8 +563,8 @@ __device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<D, NS>& s,
         if (!mbar_wait(&s.kv_empty[slot], phase, ctx, kRoleTma)) return false;
         mbar_arrive_expect_tx(&s.kv_full[slot], kTileBytes);
 #pragma unroll
-        for (int h = 0; h < D / 64; ++h) {
-          tma_load_4d(s.kv[slot] + h * kHalfBytes, tm, &s.kv_full[slot], h * 64, j * kTileN, it.hkv, it.b);
+        for (int h = 0; h < kSubTiles; ++h) {
+          tma_load_4d(s.kv[slot] + h * kSubBytes, tm, &s.kv_full[slot], h * kSubElems, j * kTileN, it.hkv, it.b);
         }
         if (++slot == NS) {
           slot = 0;
@@ -527,7 +590,7 @@ __device__ __forceinline__ void fa_tma_role(const FaParams& p, FaSmem<D, NS>& s,
 template <typename T, int D, int NS>
 __global__ void __launch_bounds__(kFaThreads, 1) fa_fwd_kernel(const __grid_constant__ FaParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  using Smem = FaSmem<D, NS>;
+  using Smem = FaSmem<T, D, NS>;
   Smem& s = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{&s.abort_flag, p.status};

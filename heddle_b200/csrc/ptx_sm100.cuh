@@ -11,6 +11,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -394,5 +395,13 @@ struct Pack2<__half> {
     return *reinterpret_cast<uint32_t*>(&v);
   }
 };
+
+// Four fp32 -> four e4m3 in one 32-bit word (element 0 in the low byte), round-to-nearest,
+// saturating.
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
 
 }  // namespace hb
