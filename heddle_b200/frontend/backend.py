@@ -49,8 +49,12 @@ log = logging.getLogger("heddle_b200")
 # leaves inserted into FX graphs
 # ----------------------------------------------------------------------------------------
 @torch.fx.wrap
-def _tilelang_sdpa_direct(q, k, v, is_causal=None, scale=None):
+def _tilelang_sdpa_direct(q, k, v, is_causal=None, scale=None, out_bshd=False):
     """Attention on (B, H, S, D) tensors; returns a new (B, H, Sq, D) tensor of q's dtype.
+
+    With ``out_bshd`` the result is stored as (B, Sq, H, D) and returned as its (B, H, Sq, D)
+    view, so that a following ``transpose(1, 2).reshape(B, S, H*D)`` is free (the rewrite sets
+    it when that is the only use).
 
     ``is_causal=None`` keeps the reference's rule for a direct call — causal iff
     Sq == Skv (Heddle/heddle/frontend/backend.py:215).  The graph rewrites in this module
@@ -58,7 +62,12 @@ def _tilelang_sdpa_direct(q, k, v, is_causal=None, scale=None):
     """
     if is_causal is None:
         is_causal = q.shape[2] == k.shape[2]
-    return ops.fa_fwd(q, k, v, causal=bool(is_causal), softmax_scale=scale)
+    out = None
+    if out_bshd:
+        out_dtype = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16
+        out = torch.empty((q.shape[0], q.shape[2], q.shape[1], q.shape[3]), dtype=out_dtype,
+                          device=q.device).transpose(1, 2)
+    return ops.fa_fwd(q, k, v, causal=bool(is_causal), softmax_scale=scale, out=out)
 
 
 @torch.fx.wrap
@@ -349,6 +358,18 @@ def try_fuse_h2o_attention(gm: fx.GraphModule) -> bool:
     return fused
 
 
+def _prefer_bshd_outputs(gm: fx.GraphModule) -> None:
+    """An attention leaf whose only consumer is ``transpose(1, 2)`` writes its result in that layout."""
+    for node in gm.graph.nodes:
+        if node.op != "call_function" or node.target is not _tilelang_sdpa_direct or len(node.users) != 1:
+            continue
+        user = next(iter(node.users))
+        if user.op == "call_method" and _name(user) == "transpose" and tuple(user.args[1:]) in ((1, 2), (2, 1)):
+            kw = dict(node.kwargs)
+            kw["out_bshd"] = True
+            node.kwargs = kw
+
+
 def _has_tilelang_wrapper_calls(gm: fx.GraphModule) -> bool:
     return any(n.op == "call_function" and n.target in _ATTENTION_LEAVES for n in gm.graph.nodes)
 
@@ -385,6 +406,8 @@ def tilelang_backend(gm: torch.fx.GraphModule, example_inputs: List[torch.Tensor
             fused_sdpa = _replace_expanded_attention(gm)
         fused_attention = fused_attention or fused_sdpa
     log.info("attention fused: %s", fused_attention)
+    if fused_attention:
+        _prefer_bshd_outputs(gm)
 
     if enable_gemm and (continue_after or not fused_attention):
         from .fusion import fuse_gemm_epilogues

@@ -12,7 +12,8 @@ residual add behind a projection, and RMSNorm in front of projections — folded
 ``RMSNorm(x) W^T = diag(rstd) (x (gamma * W)^T)`` with one ``hb_rms_rowstat`` pass.
 
 Passes, in order:  RMSNorm recognition -> linear(+activation) -> SwiGLU -> residual add
--> RMSNorm folding into its consumer GEMMs.
+-> RMSNorm folding into its consumer GEMMs -> rotate-half RoPE into the projection epilogue ->
+sibling projections (Q, K, V) merged into one GEMM on stacked weights.
 """
 from __future__ import annotations
 
@@ -58,12 +59,39 @@ def _stack(wg: torch.Tensor, wu: torch.Tensor) -> torch.Tensor:
     return hit
 
 
+def _stack_many(ws) -> torch.Tensor:
+    k = _key(*ws)
+    hit = _stacked.get(k)
+    if hit is None:
+        hit = torch.cat(list(ws), dim=0).contiguous()
+        _stacked[k] = hit
+    return hit
+
+
 @torch.fx.wrap
-def hb_linear(x, w, bias=None, act="none", residual=None, row_scale=None, gamma=None):
-    """act(row_scale * (x @ (gamma*w).T) + bias) + residual in one kernel."""
+def hb_linear(x, w, bias=None, act="none", residual=None, row_scale=None, gamma=None,
+              rope_cos=None, rope_sin=None, head_dim=0):
+    """act(row_scale * (x @ (gamma*w).T) + bias) + residual in one kernel; with ``rope_cos`` /
+    ``rope_sin`` ([S, head_dim/2]) the rotate-half rotary embedding is applied per head instead
+    of an activation (position = row index modulo S)."""
     if gamma is not None:
         w = _fold_gamma(w, gamma)
+    if rope_cos is not None:
+        return ops.gemm_epilogue(x, w, "rope", bias=bias, residual=residual, row_scale=row_scale,
+                                 rope=(rope_cos, rope_sin, head_dim, w.shape[0]))
     return ops.gemm_epilogue(x, w, act, bias=bias, residual=residual, row_scale=row_scale)
+
+
+@torch.fx.wrap
+def hb_linear_multi(x, ws, row_scale=None, gamma=None, rope_cos=None, rope_sin=None, head_dim=0, rope_cols=0):
+    """Several projections of one input as a single GEMM on the stacked weights (e.g. Q, K, V):
+    returns the (..., sum N_i) result; columns [0, rope_cols) carry the rotary embedding."""
+    w = _stack_many(ws)
+    if gamma is not None:
+        w = _fold_gamma(w, gamma)
+    if rope_cos is not None and rope_cols > 0:
+        return ops.gemm_epilogue(x, w, "rope", row_scale=row_scale, rope=(rope_cos, rope_sin, head_dim, rope_cols))
+    return ops.gemm_epilogue(x, w, "none", row_scale=row_scale)
 
 
 @torch.fx.wrap
@@ -88,7 +116,7 @@ def hb_rms_rowstat(x, eps):
     return ops.rms_rowstat(x, None, eps)[1]
 
 
-GEMM_LEAVES = (hb_linear, hb_swiglu)
+GEMM_LEAVES = (hb_linear, hb_swiglu, hb_linear_multi)
 
 
 # ----------------------------------------------------------------------------------------
@@ -308,6 +336,152 @@ def _pass_fold_rmsnorm(gm: fx.GraphModule) -> int:
     return n
 
 
+def _uncast(n):
+    """Look through ``.to(...)`` casts of a table (the kernel keeps cos / sin in fp32)."""
+    while isinstance(n, fx.Node) and n.op == "call_method":
+        dtype_only = _fname(n) == "float" or (_fname(n) == "to" and len(n.args) == 2 and not n.kwargs
+                                              and isinstance(n.args[1], torch.dtype))
+        if not dtype_only:  # a cast that also moves the table between devices stays in the graph
+            break
+        n = n.args[0]
+    return n
+
+
+def _match_rotate_half(cat: fx.Node):
+    """cat([x1*cos - x2*sin, x2*cos + x1*sin], -1) with x1, x2 the halves of x's last axis.
+    Returns (x, cos, sin, half) or None."""
+    if _fname(cat) != "cat" or not cat.args or not isinstance(cat.args[0], (list, tuple)) or len(cat.args[0]) != 2:
+        return None
+    dim = cat.args[1] if len(cat.args) > 1 else cat.kwargs.get("dim", 0)
+    lo, hi = cat.args[0]
+    if dim != -1 or _fname(lo) != "sub" or _fname(hi) != "add":
+        return None
+
+    def prod(n):
+        if _fname(n) != "mul" or len(n.args) != 2:
+            return None
+        return n.args
+
+    a, b = prod(lo.args[0]), prod(lo.args[1])       # x1*cos, x2*sin
+    c, d = prod(hi.args[0]), prod(hi.args[1])       # x2*cos, x1*sin
+    if None in (a, b, c, d):
+        return None
+    x1, cos = a
+    x2, sin = b
+    if not (c[0] is x2 and c[1] is cos and d[0] is x1 and d[1] is sin):
+        return None
+
+    def half_of(n):
+        if _fname(n) != "getitem" or len(n.args) != 2 or not isinstance(n.args[1], tuple) or len(n.args[1]) != 2:
+            return None
+        e, sl = n.args[1]
+        if e is not Ellipsis or not isinstance(sl, slice) or sl.step not in (None, 1):
+            return None
+        return n.args[0], sl.start, sl.stop
+
+    h1, h2 = half_of(x1), half_of(x2)
+    if h1 is None or h2 is None or h1[0] is not h2[0]:
+        return None
+    x = h1[0]
+    half = h1[2]
+    if h1[1] not in (None, 0) or not isinstance(half, int) or h2[1] != half or h2[2] is not None:
+        return None
+    if len(x.users) != 2 or len(x1.users) != 2 or len(x2.users) != 2:
+        return None
+    return x, cos, sin, half
+
+
+def _pass_rope(gm: fx.GraphModule) -> int:
+    """rotate-half RoPE applied to transpose(view(hb_linear(...), B, S, H, D), 1, 2) moves into the
+    projection's epilogue."""
+    n = 0
+    for cat in list(gm.graph.nodes):
+        m = _match_rotate_half(cat) if cat.op == "call_function" else None
+        if m is None:
+            continue
+        x, cos, sin, half = m
+        if _fname(x) != "transpose" or tuple(x.args[1:]) not in ((1, 2), (2, 1)):
+            continue
+        view = x.args[0]
+        if _fname(view) not in ("view", "reshape") or len(view.users) != 1:
+            continue
+        lin = view.args[0]
+        if not isinstance(lin, fx.Node) or lin.target is not hb_linear or len(lin.users) != 1:
+            continue
+        if lin.kwargs.get("act", "none") != "none" or lin.kwargs.get("residual") is not None \
+                or lin.kwargs.get("rope_cos") is not None:
+            continue
+        shp = view.args[1:] if len(view.args) > 2 else tuple(view.args[1])
+        cs = _meta_shape(cos)
+        if len(shp) != 4 or shp[3] != 2 * half or 2 * half not in (64, 128, 256) or cs is None \
+                or tuple(cs) != (shp[1], half):
+            continue
+        kwargs = dict(lin.kwargs)
+        kwargs.update(rope_cos=_uncast(cos), rope_sin=_uncast(sin), head_dim=2 * half)
+        lin.kwargs = kwargs
+        cat.replace_all_uses_with(x)
+        n += 1
+    if n:
+        # the tables may be computed after the projection in program order: re-sort topologically
+        from torch.fx.passes.tools_common import legalize_graph
+
+        legalize_graph(gm)
+        gm.graph.eliminate_dead_code()
+    return n
+
+
+def _pass_merge_siblings(gm: fx.GraphModule) -> int:
+    """Projections of the same input (same RMSNorm fold, no bias / activation / residual) become
+    one GEMM on stacked weights; rotary ones first so that they form the rotated column prefix."""
+    groups: Dict[Tuple, List[fx.Node]] = {}
+    for node in gm.graph.nodes:
+        if node.op != "call_function" or node.target is not hb_linear:
+            continue
+        kw = node.kwargs
+        if kw.get("bias") is not None or kw.get("residual") is not None or kw.get("act", "none") != "none":
+            continue
+        key = (node.args[0], kw.get("row_scale"), kw.get("gamma"))
+        groups.setdefault(key, []).append(node)
+    merged = 0
+    for (x, row_scale, gamma), nodes in groups.items():
+        if len(nodes) < 2:
+            continue
+        rot = [n for n in nodes if n.kwargs.get("rope_cos") is not None]
+        if rot and any((n.kwargs["rope_cos"], n.kwargs["rope_sin"], n.kwargs["head_dim"]) !=
+                       (rot[0].kwargs["rope_cos"], rot[0].kwargs["rope_sin"], rot[0].kwargs["head_dim"]) for n in rot):
+            continue
+        order = rot + [n for n in nodes if n not in rot]
+        widths = []
+        for n in order:
+            ws = _meta_shape(n.args[1])
+            widths.append(None if ws is None else ws[0])
+        if any(w is None for w in widths):
+            continue
+        order_in_graph = {n: i for i, n in enumerate(gm.graph.nodes)}
+        last = max(nodes, key=lambda n: order_in_graph[n])
+        kwargs = {"row_scale": row_scale, "gamma": gamma}
+        if rot:
+            kwargs.update(rope_cos=rot[0].kwargs["rope_cos"], rope_sin=rot[0].kwargs["rope_sin"],
+                          head_dim=rot[0].kwargs["head_dim"], rope_cols=sum(widths[:len(rot)]))
+        # created where the last sibling stood (all operands are defined there); users of earlier
+        # siblings are moved behind it by the topological re-sort below
+        with gm.graph.inserting_before(last):
+            big = gm.graph.call_function(hb_linear_multi, (x, [n.args[1] for n in order]), kwargs)
+            col = 0
+            for n, w in zip(order, widths):
+                part = gm.graph.call_function(operator.getitem, (big, (Ellipsis, slice(col, col + w))))
+                part.meta = dict(n.meta)
+                n.replace_all_uses_with(part)
+                col += w
+        merged += 1
+    if merged:
+        from torch.fx.passes.tools_common import legalize_graph
+
+        legalize_graph(gm)
+        gm.graph.eliminate_dead_code()
+    return merged
+
+
 def fuse_gemm_epilogues(gm: fx.GraphModule) -> int:
     """Run all passes; returns the number of GEMM leaves in the rewritten graph."""
     _pass_rmsnorm(gm)
@@ -315,6 +489,8 @@ def fuse_gemm_epilogues(gm: fx.GraphModule) -> int:
     _pass_swiglu(gm)
     _pass_residual(gm)
     _pass_fold_rmsnorm(gm)
+    _pass_rope(gm)
+    _pass_merge_siblings(gm)
     gm.graph.lint()
     gm.recompile()
     return sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target in GEMM_LEAVES)

@@ -202,13 +202,17 @@ def test_llama_layer_lowering():
     t = targets(gm)
     assert t.count(B._tilelang_sdpa_direct) == 1
     assert t.count(fusion.hb_swiglu) == 1
-    assert t.count(fusion.hb_linear) == 5          # wq, wk, wv, wo, w_down
+    assert t.count(fusion.hb_linear_multi) == 1    # wq, wk, wv as one GEMM
+    assert t.count(fusion.hb_linear) == 2          # wo, w_down
     assert t.count(fusion.hb_rms_rowstat) == 2     # one statistic per RMSNorm
     assert fusion.hb_rmsnorm not in t              # both norms folded into their GEMMs
+    assert not any(getattr(x, "__name__", "") == "cat" for x in t)            # RoPE moved into the epilogue
     lin = [n for n in gm.graph.nodes if n.target is fusion.hb_linear]
     assert sum(1 for n in lin if n.kwargs.get("residual") is not None) == 2   # wo and w_down
-    assert sum(1 for n in lin if n.kwargs.get("row_scale") is not None) == 3  # q, k, v projections
+    qkv = next(n for n in gm.graph.nodes if n.target is fusion.hb_linear_multi)
+    assert len(qkv.args[1]) == 3 and qkv.kwargs["rope_cols"] == 512 and qkv.kwargs["head_dim"] == 128
+    assert qkv.kwargs.get("row_scale") is not None and qkv.kwargs.get("gamma") is not None
     sw = next(n for n in gm.graph.nodes if n.target is fusion.hb_swiglu)
     assert sw.kwargs.get("row_scale") is not None and sw.kwargs.get("gamma") is not None
     sd = next(n for n in gm.graph.nodes if n.target is B._tilelang_sdpa_direct)
-    assert sd.kwargs["is_causal"] is True
+    assert sd.kwargs["is_causal"] is True and sd.kwargs.get("out_bshd") is True

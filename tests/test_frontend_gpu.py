@@ -80,3 +80,33 @@ def test_mlp_block_matches_oracle_epilogues(backend):
     with torch.no_grad():
         out = _compile(m.cuda(), backend)(x.cuda())
     assert (out.float().cpu() - ref.float()).abs().max().item() <= 3e-2
+
+
+def test_full_size_llama_layer(backend):
+    """The fused-layer configuration at full size: hidden 4096, 32 heads of 128, SwiGLU 11008, eps 1e-5,
+    theta 10000, batch 8 x seq 2048, weights N(0, 0.02), activations N(0, 1), bf16.  The whole batch runs
+    through the compiled layer; batch element 0 is checked against the fp32 eager module on the CPU
+    (the layer is data-parallel over batch), every element for finiteness and batch-independence."""
+    layer = O.LlamaLayer().init_weights(seed=0).to(torch.bfloat16)
+    x = torch.randn(8, 2048, 4096, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    with torch.no_grad():
+        out = _compile(copy_to_cuda(layer), backend)(x.cuda())
+        torch.cuda.synchronize()
+        assert out.shape == x.shape and torch.isfinite(out.float()).all()
+        ref_layer = O.LlamaLayer().init_weights(seed=0)
+        for p in ref_layer.parameters():
+            p.data = p.data.to(torch.bfloat16).float()
+        ref = ref_layer(x[:1].float())
+    err = (out[:1].float().cpu() - ref).abs().max().item()
+    assert err <= 2e-2 * max(1.0, ref.abs().max().item()), err
+    # the same sequence placed at another batch index gives the same rows
+    with torch.no_grad():
+        x2 = x.clone()
+        x2[5] = x[0]
+        out2 = _compile(copy_to_cuda(layer), backend)(x2.cuda())
+    assert torch.equal(out2[5], out[0])
+
+
+def copy_to_cuda(module):
+    import copy
+    return copy.deepcopy(module).cuda()
