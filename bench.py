@@ -132,10 +132,22 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------
 # CPU legs (the oracle is only ever the thing compared against or timed as the baseline)
 # ----------------------------------------------------------------------------------------
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs use every core this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_slice_tflops(heads: int = 2, reps: int = 3):
     """Reference eager fp32 attention on the host cores for a slice of the workload:
     one batch element x ``heads`` query heads at full sequence length."""
     from oracle import attention_oracle as O
+
+    use_all_host_threads()
 
     S, D = WORKLOAD["S"], WORKLOAD["D"]
     q, k, v = O.make_qkv(1, heads, heads, S, S, D, seed=0, dtype=torch.bfloat16)
@@ -158,6 +170,7 @@ def run_reference(args):
         return
     heads = 2
     from oracle import attention_oracle as O
+    use_all_host_threads()
     S, D = WORKLOAD["S"], WORKLOAD["D"]
     q, k, v = O.make_qkv(1, heads, heads, S, S, D, seed=0, dtype=torch.bfloat16)
     steps = max(1, min(args.steps, 20))
