@@ -1,0 +1,135 @@
+"""Device-resident timings of the secondary configurations (one JSON line each):
+
+    python -m heddle_b200.bench_configs --config c3|c4|c5|gemm|h2o [--steps N] [--warmup W]
+
+  c3    BF16 causal GQA, one GPU's share of B=8 Hq=64 Hkv=8 S=8192 D=128 at 8 GPUs
+        (one KV head with its 8 query heads, all 8 batches)
+  c4    FP8 e4m3 non-causal, B=4 H=32 S=8192 D=128, per-tensor scales amax/448
+  c5    Llama-style decoder layer through torch.compile(backend=tilelang_backend):
+        hidden 4096, 32 x 128 heads, SwiGLU 11008, B=8 S=2048, bf16
+  gemm  the layer's gate/up projection as one SwiGLU GEMM: M=16384 N=2x11008 K=4096
+  h2o   H2O score on the headline attention shape (B=4 H=32 S=4096 D=128, causal)
+
+``bench.py`` carries the headline metric; this module exists so that every kernel has a
+one-command workload for timing and profiling.  Inputs are synthetic N(0,1) / N(0,0.02).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def _time(fn, steps: int, warmup: int) -> float:
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", choices=["c3", "c4", "c5", "gemm", "h2o"], required=True)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device: the heddle_b200 kernels have no CPU path")
+    from . import ops
+
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, generator=gen, device="cuda")
+    line = {"config": args.config, "steps": args.steps, "unit": "TFLOP/s", "data": "synthetic"}
+    if args.config == "c3":
+        B, Hq, Hkv, S, D = 8, 8, 1, 8192, 128
+        q, k, v = rnd(B, Hq, S, D).bfloat16(), rnd(B, Hkv, S, D).bfloat16(), rnd(B, Hkv, S, D).bfloat16()
+        ms = _time(lambda: ops.fa_fwd(q, k, v, causal=True), args.steps, args.warmup)
+        flops = 2.0 * B * Hq * S * S * D
+        line.update(workload="bf16_causal_gqa_B8_Hq8_Hkv1_S8192_D128 (1/8 of config 3)", dtype="bf16")
+    elif args.config == "c4":
+        B, H, S, D = 4, 32, 8192, 128
+        q, k, v = rnd(B, H, S, D), rnd(B, H, S, D), rnd(B, H, S, D)
+        sc = [float(t.abs().max()) / 448.0 for t in (q, k, v)]
+        qq, kq, vq = ((t / s).to(torch.float8_e4m3fn) for t, s in zip((q, k, v), sc))
+        del q, k, v
+        ms = _time(lambda: ops.fa_fwd(qq, kq, vq, causal=False, scales=sc), args.steps, args.warmup)
+        flops = 4.0 * B * H * S * S * D
+        line.update(workload="fp8_e4m3_noncausal_B4_H32_S8192_D128", dtype="e4m3")
+    elif args.config == "h2o":
+        B, H, S, D = 4, 32, 4096, 128
+        q, k, v = rnd(B, H, S, D).bfloat16(), rnd(B, H, S, D).bfloat16(), rnd(B, H, S, D).bfloat16()
+        _, lse = ops.fa_fwd(q, k, v, causal=True, return_lse=True)
+        ms = _time(lambda: ops.h2o_score(q, k, lse, causal=True), args.steps, args.warmup)
+        flops = 1.0 * B * H * S * S * D  # one causal Q K^T product
+        line.update(workload="h2o_score_bf16_causal_B4_H32_S4096_D128", dtype="bf16")
+    elif args.config == "gemm":
+        M, N, K = 16384, 2 * 11008, 4096
+        a, w = rnd(M, K).bfloat16(), (rnd(N, K) * 0.02).bfloat16()
+        ms = _time(lambda: ops.gemm_epilogue(a, w, "swiglu"), args.steps, args.warmup)
+        flops = 2.0 * M * N * K
+        line.update(workload="swiglu_gemm_M16384_N22016_K4096", dtype="bf16")
+    else:
+        import torch.nn.functional as F
+
+        from .frontend import tilelang_backend
+
+        class Layer(torch.nn.Module):
+            """Pre-norm Llama block (RMSNorm eps 1e-5, rotate-half RoPE theta 10000, causal attention, SwiGLU)."""
+
+            def __init__(self, hidden=4096, heads=32, inter=11008):
+                super().__init__()
+                lin = lambda i, o: torch.nn.Linear(i, o, bias=False)
+                self.h, self.nh, self.hd = hidden, heads, hidden // heads
+                self.wq, self.wk, self.wv, self.wo = lin(hidden, hidden), lin(hidden, hidden), lin(hidden, hidden), lin(hidden, hidden)
+                self.wg, self.wu, self.wd = lin(hidden, inter), lin(hidden, inter), lin(inter, hidden)
+                self.g1, self.g2 = torch.nn.Parameter(torch.ones(hidden)), torch.nn.Parameter(torch.ones(hidden))
+
+            def rms(self, x, g):
+                return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * g
+
+            def rope(self, x, cos, sin):
+                d = self.hd // 2
+                x1, x2 = x[..., :d], x[..., d:]
+                return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+            def forward(self, x):
+                B, S, _ = x.shape
+                h = self.rms(x, self.g1)
+                q, k, v = (w(h).view(B, S, self.nh, self.hd).transpose(1, 2) for w in (self.wq, self.wk, self.wv))
+                inv = 1.0 / (10000.0 ** (torch.arange(0, self.hd, 2, dtype=torch.float32, device=x.device) / self.hd))
+                ang = torch.arange(S, dtype=torch.float32, device=x.device)[:, None] * inv[None, :]
+                cos, sin = torch.cos(ang).to(x.dtype), torch.sin(ang).to(x.dtype)
+                a = F.scaled_dot_product_attention(self.rope(q, cos, sin), self.rope(k, cos, sin), v, is_causal=True)
+                x = x + self.wo(a.transpose(1, 2).reshape(B, S, self.h))
+                h = self.rms(x, self.g2)
+                return x + self.wd(F.silu(self.wg(h)) * self.wu(h))
+
+        torch.manual_seed(0)
+        layer = Layer()
+        with torch.no_grad():
+            for prm in layer.parameters():
+                if prm.dim() == 2:
+                    prm.normal_(0.0, 0.02)
+        layer = layer.to(torch.bfloat16).cuda()
+        x = rnd(8, 2048, 4096).bfloat16()
+        with torch.no_grad():
+            eager_ms = _time(lambda: layer(x), args.steps, args.warmup)
+            torch._dynamo.reset()
+            comp = torch.compile(layer, backend=tilelang_backend)
+            ms = _time(lambda: comp(x), args.steps, args.warmup)
+        flops = 6.907e12
+        line.update(workload="llama_layer_h4096_heads32_inter11008_B8_S2048", dtype="bf16", eager_pytorch_ms=eager_ms,
+                    eager_pytorch_tflops=flops / eager_ms / 1e9)
+    line.update(ms=ms, value=flops / ms / 1e9, algorithmic_tflop=flops / 1e12, device_status_word=ops.status_word())
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()
