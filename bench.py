@@ -162,6 +162,49 @@ def cpu_slice_tflops(heads: int = 2, reps: int = 3):
     return fl / t / 1e12, t, f"B=1 x {heads} heads x S={S} D={D} causal, eager fp32, median of {reps}"
 
 
+def reference_gpu_kernel(B, H, S, D, causal):
+    """The reference's own generated kernel on this GPU, when its package is present under
+    baseline/_ref (a git-ignored pip --target install of the reference) and TileLang can JIT it:
+    Heddle's `_build_fa_kernel` template (fp16, the only dtype it has; tile 128x128, 2 stages, 256
+    threads = its heuristic's choice), timed with the reference's own protocol (10 warm-up, 50
+    launches, CUDA events, median).  Any failure is reported, never fatal."""
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "heddle").exists():
+        return {"unavailable": "baseline/_ref/heddle not present"}
+    try:
+        os.environ.setdefault("TILELANG_DISABLE_CACHE", "1")
+        sys.path.insert(0, str(ref_dir))
+        import contextlib
+        import io
+
+        with contextlib.redirect_stdout(io.StringIO()):
+            import heddle
+            heddle.init()
+            from heddle.frontend.backend import _build_fa_kernel
+            kern = _build_fa_kernel(B, H, S, S, D, is_causal=causal, block_M=128, block_N=128, num_stages=2, threads=256)
+        g = torch.Generator(device="cuda").manual_seed(7)
+        q, k, v = (torch.randn(B, H, S, D, generator=g, device="cuda").to(torch.float16) for _ in range(3))
+        for _ in range(10):
+            kern(q, k, v)
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(50):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            kern(q, k, v)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        ms = statistics.median(times)
+        return {"value": algorithmic_flops(B, H, S, D, causal) / (ms * 1e-3) / 1e12, "unit": UNIT, "ms": ms,
+                "dtype": "fp16", "what": "Heddle _build_fa_kernel through TileLang JIT (mma.sync path), median of 50"}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+    finally:
+        if str(ref_dir) in sys.path:
+            sys.path.remove(str(ref_dir))
+
+
 def run_reference(args):
     """Reference arm: the reference's CPU implementation of the path (its FX graph run
     eagerly in fp32 = the oracle port), all host threads, bounded sample per step."""
@@ -346,6 +389,10 @@ def run_ours(args):
         cpu = {"value": v_cpu, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                "sample": sample + f" ({t_cpu:.3f} s per slice)"}
 
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.kernel_only and not args.no_reference_gpu:
+        ref_gpu = reference_gpu_kernel(B, H, S, D, causal)
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -355,7 +402,7 @@ def run_ours(args):
                        "heads": H, "head_dim": D, "causal": True, "parallelism": f"dp{world}_batch_x_head_no_collective",
                        "l2": "inputs+outputs (268 MB per step) exceed the 126 MB L2; no explicit flush"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * world,
-            "clocks": clocks.summary(), "device_status_word": status,
+            "clocks": clocks.summary(), "device_status_word": status, "reference_gpu_kernel": ref_gpu,
             "pct_of_nominal_dense_bf16_peak_2250": 100.0 * value / world / 2250.0,
         }
         print(json.dumps(line), flush=True)
@@ -369,6 +416,8 @@ def main():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-reference-gpu", action="store_true",
+                    help="skip timing the reference's own generated kernel (needs baseline/_ref and TileLang)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
     args = ap.parse_args()
