@@ -225,49 +225,43 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<T, D, 
         }
         HB_TRACE(p, warp, 3);
 
-        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-        if constexpr (!FaTraits<T>::kFp8) {
+        // p = exp2(s * scale - m): scale-and-subtract and the row sum run on packed fp32 pairs
+        // (half the FMA-pipe instructions), the exponentials on the MUFU, one per score.
+        float sum0, sum1, sum2, sum3;
+        {
+          const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_scaled, -m_scaled);
+          uint64_t sa = pack_f32x2(0.f, 0.f), sb = pack_f32x2(0.f, 0.f);
+          constexpr int kChunk = FaTraits<T>::kFp8 ? 64 : 32;  // scores per 16 packed TMEM columns
 #pragma unroll
-          for (int q = 0; q < kTileN / 32; ++q) {
+          for (int q = 0; q < kTileN / kChunk; ++q) {
             uint32_t pk[16];
 #pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              float pe[8];
-#pragma unroll
-              for (int u = 0; u < 8; ++u) pe[u] = fmaf(__uint_as_float(v[q * 32 + e + u]), scale_log2, -m_scaled);
-#pragma unroll
-              for (int u = 0; u < 8; ++u) pe[u] = fast_exp2(pe[u]);
-              sum0 += pe[0] + pe[4];
-              sum1 += pe[1] + pe[5];
-              sum2 += pe[2] + pe[6];
-              sum3 += pe[3] + pe[7];
-#pragma unroll
-              for (int u = 0; u < 8; u += 2) pk[(e + u) / 2] = Pack2<T>::pack(pe[u], pe[u + 1]);
+            for (int e = 0; e < kChunk; e += 4) {
+              const int c = q * kChunk + e;
+              const uint64_t x0 = fma_f32x2(pack_f32x2(__uint_as_float(v[c]), __uint_as_float(v[c + 1])), sc2, nm2);
+              const uint64_t x1 = fma_f32x2(pack_f32x2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])), sc2, nm2);
+              float a0, a1, b0, b1;
+              unpack_f32x2(x0, a0, a1);
+              unpack_f32x2(x1, b0, b1);
+              a0 = fast_exp2(a0);
+              a1 = fast_exp2(a1);
+              b0 = fast_exp2(b0);
+              b1 = fast_exp2(b1);
+              sa = add_f32x2(sa, pack_f32x2(a0, a1));
+              sb = add_f32x2(sb, pack_f32x2(b0, b1));
+              if constexpr (FaTraits<T>::kFp8) {
+                // e4m3 P: four values per TMEM column, scaled by kPScale (a power of two, exact)
+                constexpr float ps = FaTraits<T>::kPScale;
+                pk[e / 4] = pack4_e4m3(a0 * ps, a1 * ps, b0 * ps, b1 * ps);
+              } else {
+                pk[e / 2] = Pack2<T>::pack(a0, a1);
+                pk[e / 2 + 1] = Pack2<T>::pack(b0, b1);
+              }
             }
             tmem_st16(tS + q * 16, pk);
           }
-        } else {
-          // e4m3 P: four values per TMEM column, scaled by kPScale (a power of two, exact)
-#pragma unroll
-          for (int q = 0; q < kTileN / 64; ++q) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int e = 0; e < 64; e += 8) {
-              float pe[8];
-#pragma unroll
-              for (int u = 0; u < 8; ++u) pe[u] = fmaf(__uint_as_float(v[q * 64 + e + u]), scale_log2, -m_scaled);
-#pragma unroll
-              for (int u = 0; u < 8; ++u) pe[u] = fast_exp2(pe[u]);
-              sum0 += pe[0] + pe[4];
-              sum1 += pe[1] + pe[5];
-              sum2 += pe[2] + pe[6];
-              sum3 += pe[3] + pe[7];
-              constexpr float ps = FaTraits<T>::kPScale;
-              pk[e / 4] = pack4_e4m3(pe[0] * ps, pe[1] * ps, pe[2] * ps, pe[3] * ps);
-              pk[e / 4 + 1] = pack4_e4m3(pe[4] * ps, pe[5] * ps, pe[6] * ps, pe[7] * ps);
-            }
-            tmem_st16(tS + q * 16, pk);
-          }
+          unpack_f32x2(sa, sum0, sum1);
+          unpack_f32x2(sb, sum2, sum3);
         }
         l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
         HB_TRACE(p, warp, 4);
