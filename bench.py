@@ -302,7 +302,13 @@ def run_ours(args):
     torch.cuda.synchronize()
     launch_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
     peaks = load_peaks()
-    sustained_run = ms_total > 1000.0
+    # Which measured peak applies: the burst figure for a kernel timed alone at full clocks, the
+    # sustained one when the timed region ran under the power cap (reduced SM clock), as a long
+    # back-to-back loop does on this 1 kW part.  Both fractions are reported.
+    clk = clocks.summary()
+    capped = "sw_power_cap" in clk["reasons"] or (clk["sm_mhz"] is not None and clk["sm_max_mhz"]
+                                                  and clk["sm_mhz"] < 0.92 * clk["sm_max_mhz"])
+    sustained_run = ms_total > 1000.0 or capped
     peak = peaks["sustained"] if sustained_run else peaks["burst"]
     achieved = flops_rank / (launch_ms * 1e-3) / 1e12
     traffic = None
@@ -314,8 +320,10 @@ def run_ours(args):
             traffic = None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": traffic, "kernel": "fa_fwd_kernel<bf16,128>",
-                "peak_kind": f"{'sustained' if sustained_run else 'burst'} dense bf16, of {peaks['source']}",
-                "frac_of_burst_peak": achieved / peaks["burst"], "launch_ms": launch_ms}
+                "peak_kind": f"{'sustained (power-capped clocks during the timed region)' if sustained_run else 'burst'}"
+                             f" dense bf16, of {peaks['source']}",
+                "frac_of_burst_peak": achieved / peaks["burst"], "frac_of_sustained_peak": achieved / peaks["sustained"],
+                "launch_ms": launch_ms}
 
     # ---- end to end through the public op with host buffers --------------------------------
     # Every step moves that step's q, k, v from pinned host memory to the device and its O and
