@@ -56,18 +56,25 @@ struct FaTraits<__nv_fp8_e4m3> {
 };
 
 // Optional phase tracing (compiled in with -DHB_FA_TRACE only): lane 0 of selected warps of
-// CTA 0 appends (clock64 << 8 | code) records to a caller-provided buffer, 4096 slots per region.
+// CTA 0 appends (clock64 << 8 | code) records to a caller-provided, zero-filled buffer, 4096 slots
+// per region (slot 0 unused); region 15 holds the CTA's start and end clocks.  A record costs
+// roughly 100-150 cycles, so compare traces only with traces of the same mask.
 #ifdef HB_FA_TRACE
-#define HB_TRACE_DECL uint32_t hb_trace_n = 0;
-#define HB_TRACE(p, region, code)                                                                        \
-  do {                                                                                                   \
-    if ((p).trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && hb_trace_n < 4094) {       \
-      (p).trace[(region) * 4096 + 1 + hb_trace_n] = (static_cast<unsigned long long>(clock64()) << 8) | (code); \
-      (p).trace[(region) * 4096] = ++hb_trace_n;                                                         \
-    }                                                                                                    \
+#ifndef HB_TRACE_MASK
+#define HB_TRACE_MASK 0xffffffffu  // bit c set: records with code c are kept
+#endif
+#define HB_TRACE_DECL(p, region)                                                                          \
+  unsigned long long* hb_tr =                                                                             \
+      ((p).trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0) ? (p).trace + (region) * 4096 + 1 : nullptr; \
+  unsigned long long* const hb_tr_end = hb_tr + 4090;
+#define HB_TRACE(p, region, code)                                                           \
+  do {                                                                                      \
+    if (((HB_TRACE_MASK >> (code)) & 1u) && hb_tr != nullptr && hb_tr < hb_tr_end) {        \
+      *hb_tr++ = (static_cast<unsigned long long>(clock64()) << 8) | (code);                \
+    }                                                                                       \
   } while (0)
 #else
-#define HB_TRACE_DECL
+#define HB_TRACE_DECL(p, region)
 #define HB_TRACE(p, region, code) \
   do {                            \
   } while (0)
@@ -155,7 +162,7 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<T, D, 
   const uint32_t tS = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(i * kTileN);
   const float scale_log2 = p.scale_log2;
   uint32_t s_cnt = 0, p_cnt = 0;  // completed s_full waits / own p_full arrivals
-  HB_TRACE_DECL
+  HB_TRACE_DECL(p, warp)
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
     for (int half = 0; half < 2; ++half) {
@@ -296,7 +303,7 @@ __device__ __forceinline__ void fa_correction_role(const FaParams& p, FaSmem<T, 
   const int row = threadIdx.x & (kTileM - 1);
   const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
   uint32_t c_cnt[2] = {0, 0}, o_cnt[2] = {0, 0};
-  HB_TRACE_DECL
+  HB_TRACE_DECL(p, warp)
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
     for (int half = 0; half < 2; ++half) {
@@ -459,7 +466,7 @@ __device__ __forceinline__ void fa_mma_role(const FaParams& p, FaSmem<T, D, NS>&
     }
   };
   uint32_t q_phase = 0, p_phase = 0;  // bit i = parity of tile i's barrier
-  HB_TRACE_DECL
+  HB_TRACE_DECL(p, 12)
 
   for (int g = blockIdx.x; g < p.total_pairs; g += gridDim.x) {
     for (int half = 0; half < 2; ++half) {
@@ -621,6 +628,9 @@ __global__ void __launch_bounds__(kFaThreads, 1) fa_fwd_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem = s.tmem_base;
   const bool run = (s.abort_flag == 0);
+#ifdef HB_FA_TRACE
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[15 * 4096 + 1] = clock64();
+#endif
 
   if (warp < 8) {
     reg_inc<184>();
@@ -646,6 +656,9 @@ __global__ void __launch_bounds__(kFaThreads, 1) fa_fwd_kernel(const __grid_cons
 
   tc_fence_before();
   __syncthreads();
+#ifdef HB_FA_TRACE
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[15 * 4096 + 2] = clock64();
+#endif
   if (warp == 12) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
