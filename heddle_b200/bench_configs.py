@@ -1,6 +1,6 @@
 """Device-resident timings of the secondary configurations (one JSON line each):
 
-    python -m heddle_b200.bench_configs --config c3|c4|c5|gemm|h2o [--steps N] [--warmup W]
+    python -m heddle_b200.bench_configs --config c3|c4|c5|gemm|h2o|rowstat [--steps N] [--warmup W]
 
   c3    BF16 causal GQA, one GPU's share of B=8 Hq=64 Hkv=8 S=8192 D=128 at 8 GPUs
         (one KV head with its 8 query heads, all 8 batches)
@@ -9,6 +9,8 @@
         hidden 4096, 32 x 128 heads, SwiGLU 11008, B=8 S=2048, bf16
   gemm  the layer's gate/up projection as one SwiGLU GEMM: M=16384 N=2x11008 K=4096
   h2o   H2O score on the headline attention shape (B=4 H=32 S=4096 D=128, causal)
+  rowstat  RMSNorm row statistic fused with the residual add on the layer's activations
+        (16384 x 4096 bf16): HBM-bound, reported in GB/s of algorithmic bytes
 
 ``bench.py`` carries the headline metric; this module exists so that every kernel has a
 one-command workload for timing and profiling.  Inputs are synthetic N(0,1) / N(0,0.02).
@@ -36,7 +38,7 @@ def _time(fn, steps: int, warmup: int) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", choices=["c3", "c4", "c5", "gemm", "h2o"], required=True)
+    ap.add_argument("--config", choices=["c3", "c4", "c5", "gemm", "h2o", "rowstat"], required=True)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -69,6 +71,29 @@ def main() -> None:
         ms = _time(lambda: ops.h2o_score(q, k, lse, causal=True), args.steps, args.warmup)
         flops = 1.0 * B * H * S * S * D  # one causal Q K^T product
         line.update(workload="h2o_score_bf16_causal_B4_H32_S4096_D128", dtype="bf16")
+    elif args.config == "rowstat":
+        M, N = 16384, 4096
+        # several activation buffers in rotation so that no launch finds its input in L2 (126 MB)
+        xs = [rnd(M, N).bfloat16() for _ in range(4)]
+        rs = [rnd(M, N).bfloat16() for _ in range(4)]
+        it = [0]
+
+        def fused():
+            i = it[0] = (it[0] + 1) % 4
+            ops.rms_rowstat(xs[i], rs[i])
+
+        def plain():
+            i = it[0] = (it[0] + 1) % 4
+            ops.rms_rowstat(xs[i])
+
+        ms_plain = _time(plain, args.steps, args.warmup)
+        ms = _time(fused, args.steps, args.warmup)
+        bytes_fused, bytes_plain = 3.0 * M * N * 2 + 4.0 * M, 1.0 * M * N * 2 + 4.0 * M
+        line.update(workload="rms_rowstat_residual_M16384_N4096", dtype="bf16", unit="GB/s", ms=ms, value=bytes_fused / ms / 1e6,
+                    algorithmic_mb=bytes_fused / 1e6, plain_statistic_ms=ms_plain, plain_statistic_gbs=bytes_plain / ms_plain / 1e6,
+                    device_status_word=ops.status_word())
+        print(json.dumps(line), flush=True)
+        return
     elif args.config == "gemm":
         M, N, K = 16384, 2 * 11008, 4096
         a, w = rnd(M, K).bfloat16(), (rnd(N, K) * 0.02).bfloat16()

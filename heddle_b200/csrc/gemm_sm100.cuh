@@ -403,6 +403,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
 // RMSNorm row statistic fused with the residual add (HBM-bound): one warp per row.
 //   y = x (+ residual), rounded to T;  rstd[m] = rsqrt(mean(y^2) + eps)
 // ------------------------------------------------------------------------------------------
+// 16-byte read-once load that does not displace L1 lines
+template <typename T>
+__device__ __forceinline__ uint4 ld_stream(const T* ptr) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr));
+  return v;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) rms_rowstat_kernel(const T* __restrict__ x, const T* __restrict__ residual,
                                                           T* __restrict__ y_out, float* __restrict__ rstd, int M,
@@ -414,12 +424,12 @@ __global__ void __launch_bounds__(256) rms_rowstat_kernel(const T* __restrict__ 
   const T* rr = residual != nullptr ? residual + (long long)row * ldx : nullptr;
   T* yr = y_out != nullptr ? y_out + (long long)row * ldx : nullptr;
   float acc = 0.f;
-  for (int c = lane * 8; c < N; c += 32 * 8) {
+  auto consume = [&](const uint4& xv, const uint4& rv, int c) {
     float v[8];
-    unpack8<T>(*reinterpret_cast<const uint4*>(xr + c), v);
+    unpack8<T>(xv, v);
     if (rr != nullptr) {
       float r[8];
-      unpack8<T>(*reinterpret_cast<const uint4*>(rr + c), r);
+      unpack8<T>(rv, r);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] += r[e];
     }
@@ -429,6 +439,26 @@ __global__ void __launch_bounds__(256) rms_rowstat_kernel(const T* __restrict__ 
     unpack8<T>(packed, w);  // statistics of the rounded values, as a consumer of y sees them
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc += w[e] * w[e];
+  };
+  // four 16-byte loads per operand in flight per lane (1 KB per warp and operand) before any use
+  constexpr int kStride = 32 * 8, kBatch = 4;
+  int c = lane * 8;
+  for (; c + (kBatch - 1) * kStride < N; c += kBatch * kStride) {
+    uint4 xv[kBatch], rv[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) xv[u] = ld_stream(xr + c + u * kStride);
+    if (rr != nullptr) {
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) rv[u] = ld_stream(rr + c + u * kStride);
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) consume(xv[u], rv[u], c + u * kStride);
+  }
+  for (; c < N; c += kStride) {
+    const uint4 xv = ld_stream(xr + c);
+    uint4 rv = xv;
+    if (rr != nullptr) rv = ld_stream(rr + c);
+    consume(xv, rv, c);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);

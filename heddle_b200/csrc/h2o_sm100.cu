@@ -7,11 +7,13 @@
 // transposed, S^T = K Q^T, so that a key is a TMEM lane: each thread owns one key, the sum
 // over queries is a plain per-thread accumulation and needs no cross-thread reduction.
 //
-// CTA (384 threads), one 128-key tile of one (batch, head) at a time:
-//   warp 0      TMA: the K tile (A operand) once per work item, a ring of Q tiles (B operand)
-//   warp 1      MMA: tcgen05.mma M=128 (keys) N=128 (queries), two TMEM accumulator buffers
-//   warps 4-7   consumer group 0: even query tiles      exp2(s*scale*log2e - LSE*log2e), masks,
-//   warps 8-11  consumer group 1: odd query tiles       per-key running sum
+// CTA (320 threads), one 128-key tile of one (batch, head) at a time:
+//   warps 0-3   consumer group 0: even query tiles      exp2(s*scale*log2e - LSE*log2e), masks,
+//   warps 4-7   consumer group 1: odd query tiles       per-key running sum
+//   warp 8      TMA: the K tile (A operand) once per work item, a ring of Q tiles (B operand)
+//   warp 9      MMA: tcgen05.mma M=128 (keys) N=128 (queries), two TMEM accumulator buffers
+// Each consumer warp stages the 128 LSE values of its query tile in shared memory (prefetched one
+// tile ahead) and reads them back as broadcast 16-byte loads.
 #include "host_common.h"
 #include "ptx_sm100.cuh"
 
@@ -20,7 +22,7 @@
 
 namespace hb {
 
-constexpr int kH2oThreads = 384;
+constexpr int kH2oThreads = 320;
 constexpr int kH2oStages = 4;
 enum H2oRole : uint32_t { kH2oTma = 0x31, kH2oMma = 0x32, kH2oCons = 0x33, kH2oDrain = 0x34 };
 
@@ -33,8 +35,9 @@ struct alignas(64) H2oParams {
   int B, Hq, Hkv, Sq, Skv;
   int group, causal;
   int nkb;         // 128-key tiles per head
+  int npairs;      // ceil(nkb / 2)
   int nqb;         // 128-query tiles
-  int total_items; // B * Hq * nkb
+  int total_items; // B * Hq * npairs
   float scale_log2;
 };
 
@@ -45,25 +48,32 @@ struct H2oSmem {
   alignas(1024) uint8_t q[kH2oStages][kTileBytes];
   uint64_t k_full, k_empty;
   uint64_t q_full[kH2oStages], q_empty[kH2oStages];
-  uint64_t acc_full[2], acc_empty[2];
+  uint64_t acc_full[4], acc_empty[4];  // [consumer group * 2 + buffer]
   uint64_t drain;
   uint32_t tmem_base, abort_flag;
+  alignas(16) float nlse[8][2][128];  // per consumer warp, double-buffered: -LSE * log2(e) of a query tile
 };
 
 struct H2oItem {
   int b, hq, hkv, k0, qt0;  // first key, first query tile that can see this key tile
 };
 
-__device__ __forceinline__ void h2o_get_item(const H2oParams& p, int g, H2oItem& it) {
-  // heaviest key tiles first within a head (causal: low key index = most queries)
-  const int kb = g % p.nkb;
-  const int bh = g / p.nkb;
+// Entry `g` of the static work list, first (half = 0) or second key tile of the pair.  Under a
+// causal mask key tile kb is seen by nqb - qt0(kb) query tiles, so tile `pair` (many queries) and
+// tile nkb-1-pair (few) together cost the same for every pair: the persistent CTAs stay balanced.
+__device__ __forceinline__ bool h2o_get_item(const H2oParams& p, int g, int half, H2oItem& it) {
+  const int pair = g % p.npairs;
+  const int bh = g / p.npairs;
+  const int kb_hi = p.nkb - 1 - pair;
+  const int kb = half == 0 ? pair : kb_hi;
+  if (half == 1 && kb_hi == pair) return false;
   it.b = bh / p.Hq;
   it.hq = bh - it.b * p.Hq;
   it.hkv = it.hq / p.group;
   it.k0 = kb * 128;
   // h2o_attention.py:99-101: q_start = max(0, (k0 - past_len) / block_M)
   it.qt0 = p.causal ? max(0, (it.k0 - (p.Skv - p.Sq)) / 128) : 0;
+  return true;
 }
 
 template <typename T, int D>
@@ -82,7 +92,7 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
       mbar_init(&s.q_full[i], 1);
       mbar_init(&s.q_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(&s.acc_full[i], 1);
       mbar_init(&s.acc_empty[i], 4);
     }
@@ -92,8 +102,8 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
     prefetch_tensormap(&p.tm_q);
     prefetch_tensormap(&p.tm_k);
   }
-  if (warp == 1) {
-    tmem_alloc(&s.tmem_base, 256);
+  if (warp == 9) {
+    tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -104,14 +114,14 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
   constexpr uint32_t kTileBytes = Smem::kTileBytes;
   constexpr uint32_t kHalfBytes = 128 * 128;
 
-  if (warp == 0) {
+  if (warp == 8) {
     if (run && lane == 0) {
       // ---------------- TMA producer ----------------
       uint32_t st = 0, phase = 1, k_phase = 1;
       bool ok = true;
-      for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x) {
+      for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1)) {
         H2oItem it;
-        h2o_get_item(p, g, it);
+        if (!h2o_get_item(p, u >> 1, u & 1, it)) continue;
         if (!mbar_wait(&s.k_empty, k_phase, ctx, kH2oTma)) break;
         k_phase ^= 1;
         mbar_arrive_expect_tx(&s.k_full, kTileBytes);
@@ -132,7 +142,7 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 9) {
     if (run) {
       // ---------------- MMA issuer (warp-uniform, elected lane issues) ----------------
       constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, 128, 128, 0, 0);
@@ -142,15 +152,16 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
       uint32_t st = 0, phase = 0, k_phase = 0, tile_i = 0;
       bool ok = true;
       const uint32_t k_lo = (smem_u32(s.k) >> 4) | kLbo;
-      for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x) {
+      for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1)) {
         H2oItem it;
-        h2o_get_item(p, g, it);
+        if (!h2o_get_item(p, u >> 1, u & 1, it)) continue;
         if (!mbar_wait_warp(&s.k_full, k_phase, ctx, kH2oMma)) break;
         k_phase ^= 1;
         for (int qt = it.qt0; qt < p.nqb; ++qt, ++tile_i) {
-          const uint32_t acc = tile_i & 1;
+          // tile i goes to consumer group i & 1, into that group's buffer (i >> 1) & 1
+          const uint32_t acc = ((tile_i & 1u) << 1) | ((tile_i >> 1) & 1u);
           if (!mbar_wait_warp(&s.q_full[st], phase, ctx, kH2oMma) ||
-              !mbar_wait_warp(&s.acc_empty[acc], ((tile_i >> 1) & 1) ^ 1, ctx, kH2oMma)) {
+              !mbar_wait_warp(&s.acc_empty[acc], ((tile_i >> 2) & 1) ^ 1, ctx, kH2oMma)) {
             ok = false;
             break;
           }
@@ -180,52 +191,92 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
       }
     }
     __syncwarp();
-  } else if (warp >= 4 && run) {
+  } else if (warp < 8 && run) {
     // ---------------- consumers ----------------
-    const int grp = (warp - 4) >> 2;              // 0 or 1
+    const int grp = warp >> 2;                    // 0 or 1
     const int key_in_tile = (warp & 3) * 32 + lane;
-    const uint32_t tacc = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(grp * 128);
+    const uint32_t tacc = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(grp * 256);
     const int past = p.Skv - p.Sq;
-    uint32_t acc_phase = 0;
+    uint32_t cg = 0, buf = 0;  // cg: tiles this group has consumed (selects buffer and parity)
     bool ok = true;
     uint32_t tile_base = 0;  // global tile counter at the start of the item (same sequence as the MMA warp)
-    for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x) {
+    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+    for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1)) {
       H2oItem it;
-      h2o_get_item(p, g, it);
+      if (!h2o_get_item(p, u >> 1, u & 1, it)) continue;
       const int key = it.k0 + key_in_tile;
       const int ntiles = p.nqb - it.qt0;
-      float sum = 0.f;
       const float* lse_row = p.lse + (static_cast<long long>(it.b) * p.Hq + it.hq) * p.Sq;
-      for (int t = 0; t < ntiles; ++t) {
-        if (((tile_base + t) & 1u) != static_cast<uint32_t>(grp)) continue;
+      // -LSE in the exp2 domain of one query of a tile (the thread's own slot of the staging
+      // buffer); queries past Sq get -inf, so their probability is exactly 0
+      auto load_nlse = [&](int t, float (&v)[4]) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int q = (it.qt0 + t) * 128 + lane * 4 + u;
+          v[u] = (q < p.Sq) ? -__ldg(lse_row + q) * 1.4426950408889634f : -INFINITY;
+        }
+      };
+      // this group's tiles of the item: t = t_first, t_first + 2, ...
+      const int t_first = static_cast<int>((tile_base ^ static_cast<uint32_t>(grp)) & 1u);
+      uint64_t sa = pack_f32x2(0.f, 0.f), sb = pack_f32x2(0.f, 0.f);
+      float nl[4] = {0.f, 0.f, 0.f, 0.f};
+      if (t_first < ntiles) load_nlse(t_first, nl);
+      for (int t = t_first; t < ntiles; t += 2) {
+        // every warp stages its own copy of the tile's 128 LSE values (no cross-warp barrier);
+        // the next tile's values are fetched behind this tile's math
+        float4* stage = reinterpret_cast<float4*>(s.nlse[warp][buf]);
+        stage[lane] = make_float4(nl[0], nl[1], nl[2], nl[3]);
+        __syncwarp();
+        if (t + 2 < ntiles) load_nlse(t + 2, nl);
+        const float4* nl4 = stage;
+        buf ^= 1;
         const int q0 = (it.qt0 + t) * 128;
-        if (!mbar_wait_warp(&s.acc_full[grp], acc_phase, ctx, kH2oCons)) {
+        const uint32_t ab = cg & 1u;
+        if (!mbar_wait_warp(&s.acc_full[grp * 2 + ab], (cg >> 1) & 1u, ctx, kH2oCons)) {
           ok = false;
           break;
         }
-        acc_phase ^= 1;
+        ++cg;
         tc_fence_after();
-        // causal: key visible to query q iff key <= q + past  <=>  q >= key - past
-        const int q_min = p.causal ? (key - past) : 0;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tacc + c * 32, r);
-          tmem_wait_ld();
+        uint32_t r[128];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            // the LSE address is the same for every lane: one broadcast load per query
-            const int q = q0 + c * 32 + e;
-            const float lse2 = (q < p.Sq) ? __ldg(lse_row + q) * 1.4426950408889634f : INFINITY;
-            const float pr = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -lse2));
-            sum += (q >= q_min) ? pr : 0.f;
+        for (int c = 0; c < 4; ++c) tmem_ld32(tacc + ab * 128 + c * 32, &r[c * 32]);
+        tmem_wait_ld();
+        // causal: key visible to query q iff key <= q + past  <=>  q >= key - past; only the
+        // tile(s) on the diagonal need the test
+        const bool need_mask = p.causal && (q0 < it.k0 + 127 - past);
+        if (need_mask) {
+          const int q_min = key - past - q0;  // first visible query of this key, tile-relative
+#pragma unroll
+          for (int e = 0; e < 128; ++e) r[e] = (e >= q_min) ? r[e] : 0xff800000u;  // -inf -> p = 0
+        }
+#pragma unroll
+        for (int e = 0; e < 128; e += 4) {
+          const float4 l4 = nl4[e >> 2];
+          const uint64_t x0 = fma_f32x2(pack_f32x2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc2, pack_f32x2(l4.x, l4.y));
+          const uint64_t x1 = fma_f32x2(pack_f32x2(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])), sc2, pack_f32x2(l4.z, l4.w));
+          float a0, a1, b0, b1;
+          unpack_f32x2(x0, a0, a1);
+          unpack_f32x2(x1, b0, b1);
+          sa = add_f32x2(sa, pack_f32x2(fast_exp2(a0), fast_exp2(a1)));
+          if ((e & 4) != 0) {
+            // every fourth pair on the FMA pipe: two consumer warps share each MUFU, which is the
+            // busiest unit of this kernel (relative error 7.5e-5)
+            exp2_poly_f32x2(x1, b0, b1);
+            sb = add_f32x2(sb, pack_f32x2(b0, b1));
+          } else {
+            sb = add_f32x2(sb, pack_f32x2(fast_exp2(b0), fast_exp2(b1)));
           }
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s.acc_empty[grp]);
+        if (lane == 0) mbar_arrive(&s.acc_empty[grp * 2 + ab]);
       }
       tile_base += static_cast<uint32_t>(ntiles);
+      float s0, s1, s2, s3;
+      unpack_f32x2(sa, s0, s1);
+      unpack_f32x2(sb, s2, s3);
+      const float sum = (s0 + s1) + (s2 + s3);
       // the two groups add their halves into the zero-initialised output (two commutative adds)
       if (key < p.Skv) atomicAdd(p.score + (static_cast<long long>(it.b) * p.Hq + it.hq) * p.Skv + key, sum);
     }
@@ -233,9 +284,9 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 9) {
     tc_fence_after();
-    tmem_dealloc(tmem, 256);
+    tmem_dealloc(tmem, 512);
   }
 }
 
@@ -300,8 +351,9 @@ static int h2o_impl(const hb_h2o_args* a) {
   p.causal = a->causal ? 1 : 0;
   p.nkb = (a->Skv + 127) / 128;
   p.nqb = (a->Sq + 127) / 128;
-  const long long total = (long long)a->B * a->Hq * p.nkb;
-  if (total > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_h2o_score: problem too large");
+  p.npairs = (p.nkb + 1) / 2;
+  const long long total = (long long)a->B * a->Hq * p.npairs;
+  if (total > 0x3fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_h2o_score: problem too large");
   p.total_items = (int)total;
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->D);
   p.scale_log2 = scale * 1.4426950408889634f;

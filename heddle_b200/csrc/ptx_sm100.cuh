@@ -98,6 +98,26 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 
+// 2^x for a packed pair on the FMA pipe (same split and cubic as exp2_poly): two packed adds for
+// the integer part, one packed FMA for the fraction, three for the cubic, one integer add per
+// element to move the integer part into the exponent field.  Inputs below -126 (and -inf) give 2^-126.
+__device__ __forceinline__ void exp2_poly_f32x2(uint64_t x, float& o0, float& o1) {
+  float a, b;
+  unpack_f32x2(x, a, b);
+  x = pack_f32x2(fmaxf(a, -126.0f), fmaxf(b, -126.0f));
+  const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f), nmagic = pack_f32x2(-12582912.0f, -12582912.0f);
+  const uint64_t xf = add_f32x2(x, magic);
+  const uint64_t fr = fma_f32x2(add_f32x2(xf, nmagic), pack_f32x2(-1.0f, -1.0f), x);
+  uint64_t pp = fma_f32x2(fr, pack_f32x2(0.0551716685f, 0.0551716685f), pack_f32x2(0.2426111251f, 0.2426111251f));
+  pp = fma_f32x2(pp, fr, pack_f32x2(0.6932609677f, 0.6932609677f));
+  pp = fma_f32x2(pp, fr, pack_f32x2(0.9999280572f, 0.9999280572f));
+  float p0, p1, n0, n1;
+  unpack_f32x2(pp, p0, p1);
+  unpack_f32x2(xf, n0, n1);
+  o0 = __int_as_float(__float_as_int(p0) + (__float_as_int(n0) << 23));
+  o1 = __int_as_float(__float_as_int(p1) + (__float_as_int(n1) << 23));
+}
+
 __device__ __forceinline__ float fast_log2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
