@@ -252,8 +252,14 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<T, D, 
               unpack_f32x2(x1, b0, b1);
               a0 = fast_exp2(a0);
               a1 = fast_exp2(a1);
-              b0 = fast_exp2(b0);
-              b1 = fast_exp2(b1);
+              if (FaTraits<T>::kFp8 && (e & 4) != 0) {
+                // FP8: the MMAs are half as long, the softmax is what bounds the step; a quarter of
+                // the exponentials go to the FMA pipe (+2.6 % measured; no gain for 16-bit types)
+                exp2_poly_f32x2(x1, b0, b1);
+              } else {
+                b0 = fast_exp2(b0);
+                b1 = fast_exp2(b1);
+              }
               sa = add_f32x2(sa, pack_f32x2(a0, a1));
               sb = add_f32x2(sb, pack_f32x2(b0, b1));
               if constexpr (FaTraits<T>::kFp8) {

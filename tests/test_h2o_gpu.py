@@ -51,3 +51,27 @@ def test_h2o_leaf_and_factories(ops):
     assert (lse2[..., 0].cpu() - ref_lse * O.LOG2E).abs().max().item() <= 2e-3
     s2 = h2o_score(1, 2, 384, 384, 128, True)(q.cuda(), k.cuda(), lse2)
     assert torch.allclose(s2, score, rtol=1e-4, atol=1e-4)
+
+
+def test_h2o_full_length_properties(ops):
+    """Headline sequence length (S = 4096, D = 128, causal): size-independent properties over all
+    heads and oracle parity on one head."""
+    B, H, S, D = 2, 4, 4096, 128
+    q, k, v = O.make_qkv(B, H, H, S, S, D, seed=11, dtype=torch.bfloat16)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    _, lse = ops.fa_fwd(qd, kd, vd, causal=True, return_lse=True)
+    score = ops.h2o_score(qd, kd, lse, causal=True)
+    again = ops.h2o_score(qd, kd, lse, causal=True)
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    sc = score.cpu()
+    assert (sc >= 0).all()
+    # every query row hands out a total probability of 1
+    assert (sc.sum(-1) - S).abs().max().item() <= 2e-3 * S
+    # the last key is only seen by the last query, the first key by every query
+    assert (sc[..., -1] <= 1.0 + 1e-3).all() and (sc[..., 0] >= sc[..., -1]).all()
+    # two commutative atomic adds per key: the result does not depend on their order
+    assert torch.equal(score, again)
+    _, ref_lse = O.attention_eager(q[:1, :1], k[:1, :1], v[:1, :1], causal=True)
+    ref = O.h2o_score(q[:1, :1], k[:1, :1], ref_lse, causal=True)
+    assert (sc[:1, :1] - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
