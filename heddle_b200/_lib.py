@@ -75,9 +75,19 @@ class GemmArgs(C.Structure):
     ]
 
 
+class PrepareArgs(C.Structure):
+    """Mirror of hb_prepare_args."""
+    _fields_ = [
+        ("src", C.c_void_p * 4), ("rows", C.c_int32 * 4), ("ld_src", C.c_int64 * 4),
+        ("n_src", C.c_int32), ("K", C.c_int32), ("gamma", C.c_void_p), ("out", C.c_void_p),
+        ("ld_out", C.c_int64), ("dtype", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
 # every symbol include/heddle_b200.h declares
 EXPORTS = (
-    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_status_word", "hb_version",
+    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_status_word",
+    "hb_version",
     "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma",
 )
 
@@ -106,6 +116,8 @@ def load() -> C.CDLL:
     lib.hb_rms_rowstat.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                    C.c_int64, C.c_float, C.c_int32, C.c_void_p]
     lib.hb_rms_rowstat.restype = C.c_int
+    lib.hb_prepare_weight.argtypes = [C.POINTER(PrepareArgs)]
+    lib.hb_prepare_weight.restype = C.c_int
     lib.hb_status_word.argtypes = [C.POINTER(C.c_uint32)]
     lib.hb_status_word.restype = C.c_int
     lib.hb_version.argtypes = []

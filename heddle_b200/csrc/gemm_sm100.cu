@@ -164,3 +164,49 @@ int hb_rms_rowstat(const void* x, const void* residual, void* y_out, float* rstd
 }
 
 }  // extern "C"
+
+extern "C" int hb_prepare_weight(const hb_prepare_args* a) {
+  using namespace hb;
+  if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_prepare_weight: args is NULL");
+  if (a->n_src < 1 || a->n_src > 4) return set_error(HB_ERR_BAD_ARG, "hb_prepare_weight: n_src must be 1..4");
+  if (a->dtype != HB_BF16 && a->dtype != HB_FP16)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_prepare_weight: dtype %d not supported (bf16, fp16)", a->dtype);
+  if (a->K <= 0 || a->K % 8 != 0) return set_error(HB_ERR_ALIGN, "hb_prepare_weight: K must be a positive multiple of 8");
+  if (a->out == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_prepare_weight: out is NULL");
+  if (a->ld_out < a->K || a->ld_out % 8 != 0 || (reinterpret_cast<uintptr_t>(a->out) & 15) != 0)
+    return set_error(HB_ERR_ALIGN, "hb_prepare_weight: out needs 16-byte alignment and a row stride that is a multiple of 8");
+  if (a->gamma != nullptr && (reinterpret_cast<uintptr_t>(a->gamma) & 15) != 0)
+    return set_error(HB_ERR_ALIGN, "hb_prepare_weight: gamma needs 16-byte alignment");
+  PrepareParams p;
+  memset(&p, 0, sizeof(p));
+  long long rows = 0;
+  for (int i = 0; i < a->n_src; ++i) {
+    if (a->src[i] == nullptr || a->rows[i] <= 0) return set_error(HB_ERR_BAD_ARG, "hb_prepare_weight: source %d is empty", i);
+    if (a->ld_src[i] < a->K || a->ld_src[i] % 8 != 0 || (reinterpret_cast<uintptr_t>(a->src[i]) & 15) != 0)
+      return set_error(HB_ERR_ALIGN, "hb_prepare_weight: source %d needs 16-byte alignment and a row stride that is a multiple of 8", i);
+    rows += a->rows[i];
+    if (rows > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_prepare_weight: too many rows");
+    p.src[i] = a->src[i];
+    p.ld_src[i] = a->ld_src[i];
+    p.row_end[i] = static_cast<int>(rows);
+  }
+  for (int i = a->n_src; i < 4; ++i) p.row_end[i] = static_cast<int>(rows);
+  p.n_src = a->n_src;
+  p.K = a->K;
+  p.gamma = a->gamma;
+  p.out = a->out;
+  p.ld_out = a->ld_out;
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != HB_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  const long long total = rows * (a->K / 8);
+  const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, 16ll * st->sm_count));
+  if (a->dtype == HB_BF16) {
+    prepare_weight_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  } else {
+    prepare_weight_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  }
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB_OK;
+}

@@ -465,4 +465,45 @@ __global__ void __launch_bounds__(256) rms_rowstat_kernel(const T* __restrict__ 
   if (lane == 0) rstd[row] = rsqrtf(acc / (float)N + eps);
 }
 
+// ------------------------------------------------------------------------------------------
+// weight preparation: row-stack up to four [rows_i, K] matrices, optional column scale
+// ------------------------------------------------------------------------------------------
+struct PrepareParams {
+  const void* src[4];
+  long long ld_src[4];
+  int row_end[4];  // exclusive prefix sums of the row counts
+  int n_src, K;
+  const void* gamma;
+  void* out;
+  long long ld_out;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) prepare_weight_kernel(const PrepareParams p) {
+  const int chunks = p.K / 8;  // 16-byte chunks per row
+  const long long total = static_cast<long long>(p.row_end[p.n_src - 1]) * chunks;
+  for (long long idx = blockIdx.x * 256ll + threadIdx.x; idx < total; idx += 256ll * gridDim.x) {
+    const int row = static_cast<int>(idx / chunks), c = static_cast<int>(idx - static_cast<long long>(row) * chunks) * 8;
+    int which = 0, base = 0;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      if (i + 1 < p.n_src && row >= p.row_end[i]) {
+        which = i + 1;
+        base = p.row_end[i];
+      }
+    }
+    const T* srow = static_cast<const T*>(p.src[which]) + static_cast<long long>(row - base) * p.ld_src[which];
+    uint4 w = ld_stream(srow + c);
+    if (p.gamma != nullptr) {
+      float v[8], g[8];
+      unpack8<T>(w, v);
+      unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.gamma) + c), g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] *= g[e];
+      w = pack8<T>(v);
+    }
+    *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + static_cast<long long>(row) * p.ld_out + c) = w;
+  }
+}
+
 }  // namespace hb

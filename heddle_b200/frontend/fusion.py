@@ -31,40 +31,31 @@ _ACT_NAMES = {"silu": "silu", "relu": "relu", "sigmoid": "sigmoid", "tanh": "tan
 # ----------------------------------------------------------------------------------------
 # leaves
 # ----------------------------------------------------------------------------------------
-_folded: Dict[Tuple, torch.Tensor] = {}
-_stacked: Dict[Tuple, torch.Tensor] = {}
+_prepared: Dict[Tuple, torch.Tensor] = {}
 
 
-def _key(*tensors: torch.Tensor) -> Tuple:
-    return tuple((t.data_ptr(), t._version, tuple(t.shape), t.dtype) for t in tensors)
+def _key(*tensors: Optional[torch.Tensor]) -> Tuple:
+    return tuple(None if t is None else (t.data_ptr(), t._version, tuple(t.shape), t.dtype) for t in tensors)
 
 
-def _fold_gamma(w: torch.Tensor, gamma: torch.Tensor) -> torch.Tensor:
-    """gamma * W (column scaling), computed once per (weight, gamma) version."""
-    k = _key(w, gamma)
-    hit = _folded.get(k)
+def _prepare(ws, gamma: Optional[torch.Tensor]) -> torch.Tensor:
+    """The GEMM's weight operand: the given nn.Linear weights stacked along the rows ([Wg; Wu],
+    [Wq; Wk; Wv]; the reference concatenates likewise, codegen.py:1146-1152) with the RMSNorm
+    weight folded into the columns, built once per (weights, gamma) version by hb_prepare_weight."""
+    ws = tuple(ws)
+    if len(ws) == 1 and gamma is None:
+        return ws[0]
+    k = _key(*ws, gamma)
+    hit = _prepared.get(k)
     if hit is None:
-        hit = (w.float() * gamma.float()[None, :]).to(w.dtype).contiguous()
-        _folded[k] = hit
-    return hit
-
-
-def _stack(wg: torch.Tensor, wu: torch.Tensor) -> torch.Tensor:
-    """[Wg; Wu] as one [2N, K] matrix (the reference concatenates likewise, codegen.py:1146-1152)."""
-    k = _key(wg, wu)
-    hit = _stacked.get(k)
-    if hit is None:
-        hit = torch.cat([wg, wu], dim=0).contiguous()
-        _stacked[k] = hit
-    return hit
-
-
-def _stack_many(ws) -> torch.Tensor:
-    k = _key(*ws)
-    hit = _stacked.get(k)
-    if hit is None:
-        hit = torch.cat(list(ws), dim=0).contiguous()
-        _stacked[k] = hit
+        if len(ws) <= 4 and all(w.shape[1] % 8 == 0 and w.dtype in (torch.bfloat16, torch.float16) for w in ws):
+            hit = ops.prepare_weight(ws, gamma)
+        else:  # more than four matrices or an odd K: compose on the device with torch
+            hit = torch.cat(list(ws), dim=0)
+            if gamma is not None:
+                hit = (hit.float() * gamma.float()[None, :]).to(hit.dtype)
+            hit = hit.contiguous()
+        _prepared[k] = hit
     return hit
 
 
@@ -74,8 +65,7 @@ def hb_linear(x, w, bias=None, act="none", residual=None, row_scale=None, gamma=
     """act(row_scale * (x @ (gamma*w).T) + bias) + residual in one kernel; with ``rope_cos`` /
     ``rope_sin`` ([S, head_dim/2]) the rotate-half rotary embedding is applied per head instead
     of an activation (position = row index modulo S)."""
-    if gamma is not None:
-        w = _fold_gamma(w, gamma)
+    w = _prepare((w,), gamma)
     if rope_cos is not None:
         return ops.gemm_epilogue(x, w, "rope", bias=bias, residual=residual, row_scale=row_scale,
                                  rope=(rope_cos, rope_sin, head_dim, w.shape[0]))
@@ -86,9 +76,7 @@ def hb_linear(x, w, bias=None, act="none", residual=None, row_scale=None, gamma=
 def hb_linear_multi(x, ws, row_scale=None, gamma=None, rope_cos=None, rope_sin=None, head_dim=0, rope_cols=0):
     """Several projections of one input as a single GEMM on the stacked weights (e.g. Q, K, V):
     returns the (..., sum N_i) result; columns [0, rope_cols) carry the rotary embedding."""
-    w = _stack_many(ws)
-    if gamma is not None:
-        w = _fold_gamma(w, gamma)
+    w = _prepare(ws, gamma)
     if rope_cos is not None and rope_cols > 0:
         return ops.gemm_epilogue(x, w, "rope", row_scale=row_scale, rope=(rope_cos, rope_sin, head_dim, rope_cols))
     return ops.gemm_epilogue(x, w, "none", row_scale=row_scale)
@@ -97,9 +85,7 @@ def hb_linear_multi(x, ws, row_scale=None, gamma=None, rope_cos=None, rope_sin=N
 @torch.fx.wrap
 def hb_swiglu(x, wg, wu, residual=None, row_scale=None, gamma=None):
     """silu(x @ wg.T) * (x @ wu.T) in one kernel."""
-    w = _stack(wg, wu)
-    if gamma is not None:
-        w = _fold_gamma(w, gamma)
+    w = _prepare((wg, wu), gamma)
     return ops.gemm_epilogue(x, w, "swiglu", residual=residual, row_scale=row_scale)
 
 

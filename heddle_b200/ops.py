@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -214,6 +214,34 @@ def rms_rowstat(x: torch.Tensor, residual: Optional[torch.Tensor] = None, eps: f
                                               y.data_ptr() if y is not None else None, rstd.data_ptr(), M, N,
                                               x2.stride(0), float(eps), _DTYPES[x.dtype], _stream_ptr(x.device)))
     return (y.reshape(x.shape) if y is not None else None), rstd.reshape(x.shape[:-1])
+
+
+def prepare_weight(weights: "Sequence[torch.Tensor]", gamma: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Stack up to four ``[rows_i, K]`` weights along the rows and fold ``gamma`` ([K]) into the
+    columns in one pass (``hb_prepare_weight``): the operand ``gemm_epilogue`` takes for merged
+    projections, SwiGLU (``[Wg; Wu]``) and RMSNorm-folded GEMMs."""
+    ws = list(weights)
+    if not 1 <= len(ws) <= 4:
+        raise ValueError("prepare_weight takes 1 to 4 weights")
+    _require_cuda(*ws, gamma)
+    K, dt = ws[0].shape[1], ws[0].dtype
+    for w in ws:
+        if w.dim() != 2 or w.shape[1] != K or w.dtype != dt:
+            raise ValueError("prepare_weight: weights must be 2-D with the same K and dtype")
+    ws = [w if w.stride(1) == 1 else w.contiguous() for w in ws]
+    if gamma is not None:
+        gamma = gamma.to(dt).contiguous()
+    out = torch.empty((sum(w.shape[0] for w in ws), K), dtype=dt, device=ws[0].device)
+    a = _lib.PrepareArgs()
+    for i, w in enumerate(ws):
+        a.src[i], a.rows[i], a.ld_src[i] = w.data_ptr(), w.shape[0], w.stride(0)
+    a.n_src, a.K = len(ws), K
+    a.gamma = gamma.data_ptr() if gamma is not None else None
+    a.out, a.ld_out, a.dtype = out.data_ptr(), out.stride(0), _DTYPES[dt]
+    a.stream = _stream_ptr(out.device)
+    with torch.cuda.device(out.device):
+        _lib.check(_lib.load().hb_prepare_weight(C.byref(a)))
+    return out
 
 
 def h2o_score(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, causal: bool = True,

@@ -202,6 +202,31 @@ int hb_gemm_epilogue(const hb_gemm_args* args);
 int hb_rms_rowstat(const void* x, const void* residual, void* y_out, float* rstd,
                    int32_t M, int32_t N, int64_t ldx, float eps, int32_t dtype, void* stream);
 
+/*
+ * One-off weight preparation for hb_gemm_epilogue: stacks up to four nn.Linear weights [rows_i, K]
+ * along the row axis (Q|K|V for one projection GEMM, gate|up for SWIGLU) and, optionally, scales
+ * column k by gamma[k] (the RMSNorm weight folded into the GEMM):
+ *   out[off_i + r, k] = round(float(src_i[r, k]) * float(gamma[k]))
+ * Replaces the host-side weight handling of the reference's GEMM wrapper, which transposes the
+ * weight to [K, N] and caches it by data_ptr (Heddle/heddle/frontend/codegen.py:1106-1131) and
+ * concatenates gate and up weights for the dual GEMM (:1146-1152); here weights keep the [N, K]
+ * layout, so preparation is a single streaming pass.
+ */
+typedef struct hb_prepare_args {
+  const void* src[4];   /* [rows[i], K] each, row stride ld_src[i] elements */
+  int32_t rows[4];
+  int64_t ld_src[4];
+  int32_t n_src;        /* 1..4 */
+  int32_t K;            /* multiple of 8 */
+  const void* gamma;    /* [K] in the weights' dtype, or NULL */
+  void* out;            /* [sum rows, K], row stride ld_out elements */
+  int64_t ld_out;
+  int32_t dtype;        /* HB_BF16 or HB_FP16 */
+  void* stream;
+} hb_prepare_args;
+
+int hb_prepare_weight(const hb_prepare_args* args);
+
 /* Device-side status word of the current device (0 = no bounded wait ever gave up);
  * reading it synchronises the device. */
 int hb_status_word(uint32_t* out);

@@ -45,6 +45,8 @@ int main(void) {
          offsetof(hb_fa_args, q_stride_b));
   printf("%zu %zu %zu\n", sizeof(hb_gemm_args), offsetof(hb_gemm_args, row_scale), offsetof(hb_gemm_args, stream));
   printf("%zu %zu\n", sizeof(hb_h2o_args), offsetof(hb_h2o_args, stream));
+  printf("%zu %zu %zu %zu\n", sizeof(hb_prepare_args), offsetof(hb_prepare_args, ld_src), offsetof(hb_prepare_args, gamma),
+         offsetof(hb_prepare_args, stream));
   return 0;
 }'''
     with tempfile.TemporaryDirectory() as d:
@@ -60,6 +62,9 @@ int main(void) {
     assert gm == [ctypes.sizeof(_lib.GemmArgs), _lib.GemmArgs.row_scale.offset, _lib.GemmArgs.stream.offset]
     h2 = [int(x) for x in lines[2].split()]
     assert h2 == [ctypes.sizeof(_lib.H2oArgs), _lib.H2oArgs.stream.offset]
+    pw = [int(x) for x in lines[3].split()]
+    assert pw == [ctypes.sizeof(_lib.PrepareArgs), _lib.PrepareArgs.ld_src.offset, _lib.PrepareArgs.gamma.offset,
+                  _lib.PrepareArgs.stream.offset]
 
 
 def test_argument_validation_needs_no_gpu(built_lib):
@@ -85,6 +90,14 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_ERR_BAD_ARG  # null pointers
     a.Sq = 0
     assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_OK  # empty problem is a no-op
+    assert built_lib.hb_prepare_weight(None) == _lib.HB_ERR_BAD_ARG
+    w = _lib.PrepareArgs()
+    w.n_src, w.K, w.dtype = 5, 64, _lib.HB_BF16
+    assert built_lib.hb_prepare_weight(ctypes.byref(w)) == _lib.HB_ERR_BAD_ARG  # at most four matrices
+    w.n_src, w.K = 1, 60
+    assert built_lib.hb_prepare_weight(ctypes.byref(w)) == _lib.HB_ERR_ALIGN  # K % 8
+    w.K = 64
+    assert built_lib.hb_prepare_weight(ctypes.byref(w)) == _lib.HB_ERR_BAD_ARG  # null output
 
 
 def test_ops_reject_cpu_tensors(built_lib):

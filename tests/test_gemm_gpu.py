@@ -123,3 +123,30 @@ def test_full_size_projection_properties(ops):
     assert torch.equal(out2.float(), out.float() * 2)
     # deterministic
     assert torch.equal(ops.gemm_epilogue(a, w), out)
+
+
+def test_prepare_weight_stacks_and_folds(ops):
+    """hb_prepare_weight against the torch expression it replaces: bit-exact (one fp32 multiply,
+    one rounding), for one to four matrices, strided sources, with and without gamma."""
+    g = torch.Generator().manual_seed(5)
+    for dtype in (torch.bfloat16, torch.float16):
+        K = 264
+        ws = [(torch.randn(r, K, generator=g) * 0.05).to(dtype).cuda() for r in (40, 128, 8, 77)]
+        gamma = (1.0 + 0.1 * torch.randn(K, generator=g)).to(dtype).cuda()
+        for n in (1, 2, 3, 4):
+            got = ops.prepare_weight(ws[:n], gamma)
+            ref = (torch.cat(ws[:n], 0).float() * gamma.float()[None, :]).to(dtype)
+            assert torch.equal(got, ref)
+            assert torch.equal(ops.prepare_weight(ws[:n]), torch.cat(ws[:n], 0))
+        wide = (torch.randn(64, 2 * K, generator=g) * 0.05).to(dtype).cuda()
+        view = wide[:, K:]  # row stride 2K, 16-byte aligned start
+        assert torch.equal(ops.prepare_weight([view, ws[0]]), torch.cat([view, ws[0]], 0))
+    with pytest.raises(RuntimeError, match="K must be"):
+        ops.prepare_weight([torch.zeros(8, 12, dtype=torch.bfloat16, device="cuda")])
+    # the operand of a merged, RMSNorm-folded projection: same result as folding on the host
+    x = torch.randn(256, K, generator=g).to(torch.bfloat16).cuda()
+    w3 = [w.to(torch.bfloat16) for w in ws[:3]]
+    gam = gamma.to(torch.bfloat16)
+    y = ops.gemm_epilogue(x, ops.prepare_weight(w3, gam), "none")
+    ref = x.float() @ (torch.cat(w3, 0).float() * gam.float()[None, :]).to(torch.bfloat16).float().t()
+    assert (y.float() - ref).abs().max().item() <= 2e-2
