@@ -25,7 +25,7 @@
 
 namespace hb {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, two epilogue warpgroups
 constexpr int kGemmBM = 128;
 constexpr int kGemmBN = 256;
 constexpr int kGemmBK = 64;
@@ -143,16 +143,18 @@ __device__ __forceinline__ void load_bias8(const GemmParams& p, int col, float (
 }
 
 // Epilogue of one accumulator tile for the row owned by this thread.  `tacc` carries the
-// warp's TMEM lane offset and the accumulator buffer's first column.
+// warp's TMEM lane offset and the accumulator buffer's first column.  Two warpgroups share a
+// tile: `part` (0 or 1) selects this thread's half of the output columns.
 template <typename T, int EPI>
-__device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t tacc, int m0, int n0, int row_in_tile) {
+__device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t tacc, int m0, int n0, int row_in_tile,
+                                                  int part) {
   const int row = m0 + row_in_tile;
   const bool row_ok = row < p.M;
   const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
 
   if constexpr (EPI == kEpiPlain) {
 #pragma unroll 1
-    for (int c = 0; c < kGemmBN / 32; ++c) {
+    for (int c = part * (kGemmBN / 64); c < (part + 1) * (kGemmBN / 64); ++c) {
       uint32_t r[32];
       __syncwarp();  // reconverge after the predicated stores of the previous chunk
       tmem_ld32(tacc + c * 32, r);
@@ -178,7 +180,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
     }
   } else if constexpr (EPI == kEpiSwiglu) {
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = part * 2; c < part * 2 + 2; ++c) {
       uint32_t rg[32], ru[32];
       __syncwarp();
       tmem_ld32(tacc + c * 32, rg);
@@ -215,10 +217,15 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
     const int pos = row_ok ? (row % p.rope_seq) : 0;
     const float* cosr = p.rope_cos + (long long)pos * half;
     const float* sinr = p.rope_sin + (long long)pos * half;
+    // two or more heads per tile: each warpgroup takes whole heads; one 256-wide head: each takes
+    // half of the rotation pairs
+    const bool split_heads = hd <= kGemmBN / 2;
+    const int h_begin = split_heads ? part * (kGemmBN / 2) : 0, h_end = split_heads ? h_begin + kGemmBN / 2 : kGemmBN;
+    const int c_begin = split_heads ? 0 : part * (half / 2), c_end = split_heads ? half : c_begin + half / 2;
 #pragma unroll 1
-    for (int h0 = 0; h0 < kGemmBN; h0 += hd) {
+    for (int h0 = h_begin; h0 < h_end; h0 += hd) {
 #pragma unroll 1
-      for (int c = 0; c < half; c += 32) {
+      for (int c = c_begin; c < c_end; c += 32) {
         uint32_t r1[32], r2[32];
         __syncwarp();
         tmem_ld32(tacc + h0 + c, r1);
@@ -277,7 +284,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.acc_full[i], 1);
-      mbar_init(&s.acc_empty[i], 4);
+      mbar_init(&s.acc_empty[i], 8);
     }
     mbar_init(&s.drain, 1);
     fence_mbar_init();
@@ -384,7 +391,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       if (!mbar_wait_warp(&s.acc_full[acc], (tile_i >> 1) & 1, ctx, kGemmRoleEpi)) break;
       tc_fence_after();
       gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, m_t * kGemmBM, n_t * p.tile_cols,
-                                quarter * 32 + lane);
+                                quarter * 32 + lane, (warp - 2) >> 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.acc_empty[acc]);
