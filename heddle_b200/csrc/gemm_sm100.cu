@@ -58,6 +58,8 @@ static int gemm_impl(const hb_gemm_args* a) {
       return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: ROPE needs head_dim | N and head_dim | rope_cols <= N");
     if (a->rope_cos == nullptr || a->rope_sin == nullptr || a->rope_seq <= 0)
       return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: ROPE needs cos/sin tables and rope_seq > 0");
+    if ((reinterpret_cast<uintptr_t>(a->rope_cos) & 15) != 0 || (reinterpret_cast<uintptr_t>(a->rope_sin) & 15) != 0)
+      return set_error(HB_ERR_ALIGN, "hb_gemm_epilogue: ROPE tables need 16-byte alignment");
   }
   if (a->M == 0) return HB_OK;
   if (a->a == nullptr || a->w == nullptr || a->out == nullptr)

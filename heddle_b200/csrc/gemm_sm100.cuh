@@ -253,12 +253,17 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
             }
           }
           if (rotate) {
+            // eight consecutive angles as two 16-byte loads per table (rows are 16-byte aligned:
+            // head_dim / 2 is a multiple of 32)
+            const float4 c0 = *reinterpret_cast<const float4*>(cosr + c + g * 8), c1 = *reinterpret_cast<const float4*>(cosr + c + g * 8 + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(sinr + c + g * 8), s1 = *reinterpret_cast<const float4*>(sinr + c + g * 8 + 4);
+            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              const float cs = cosr[c + g * 8 + e], sn = sinr[c + g * 8 + e];
               const float a = x1[e], b = x2[e];
-              x1[e] = a * cs - b * sn;
-              x2[e] = b * cs + a * sn;
+              x1[e] = a * cs[e] - b * sn[e];
+              x2[e] = b * cs[e] + a * sn[e];
             }
           }
           store8<T>(p, row, col + g * 8, x1);
