@@ -180,3 +180,27 @@ def test_full_size_gqa_slice(ops):
     assert torch.equal(out_mha, out)
     assert (ops.fa_fwd(q, k, torch.ones_like(v), causal=True).float() - 1.0).abs().max().item() <= 1e-2
     _sampled_check(out, lse, q, k, v, True, [(0, 0), (1, 7)])
+
+
+def test_long_sequence_rows(ops):
+    """S = 32768 (256 key tiles per row block, the longest block a CTA walks): the first, a middle and
+    the last query rows against the oracle, which sees those rows as a short query block with the
+    matching causal offset; decode-shaped calls (Sq = 1 and Sq = 5 against the full keys) as well."""
+    B, H, S, D = 1, 2, 32768, 128
+    q, k, v = O.make_qkv(B, H, H, S, S, D, seed=77, dtype=torch.bfloat16)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    out, lse = ops.fa_fwd(qd, kd, vd, causal=True, return_lse=True)
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    for lo, hi in ((0, 16), (16383, 16399), (S - 16, S)):
+        # rows [lo, hi) of the causal problem = a (hi - lo)-row query block over keys [0, hi)
+        ref, ref_lse = O.attention_eager(q[:, :, lo:hi], k[:, :, :hi], v[:, :, :hi], causal=True)
+        assert (out[:, :, lo:hi].float().cpu() - ref).abs().max().item() <= 2e-2
+        assert (lse[:, :, lo:hi].cpu() - ref_lse).abs().max().item() <= 1e-3
+    for sq in (1, 5):
+        o2, l2 = ops.fa_fwd(qd[:, :, S - sq:].contiguous(), kd, vd, causal=True, return_lse=True)
+        ref, ref_lse = O.attention_eager(q[:, :, S - sq:], k, v, causal=True)
+        assert (o2.float().cpu() - ref).abs().max().item() <= 2e-2
+        assert (l2.cpu() - ref_lse).abs().max().item() <= 1e-3
+        # the same rows as part of the full problem
+        assert (o2.float() - out[:, :, S - sq:].float()).abs().max().item() <= 1e-2
