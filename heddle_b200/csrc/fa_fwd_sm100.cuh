@@ -10,7 +10,7 @@
 //   warps 4-7   softmax warpgroup for query tile 1
 //   warps 8-11  correction warpgroup: rescales O in TMEM when a row max moved,
 //               final O / l, LSE, conversion and the global store
-//   warp  12    MMA issuer: one thread issues tcgen05.mma for S = Q K^T (operands in
+//   warp  12    MMA issuer (warp-uniform loop, one elected lane issues): S = Q K^T (operands in
 //               shared memory) and O += P V (P read from TMEM, V MN-major in shared
 //               memory); accumulators live in TMEM
 //   warp  13    TMA producer: Q tiles and a ring of K/V tiles behind mbarriers

@@ -6,12 +6,13 @@
 // Heddle/heddle/frontend/codegen.py:1124-1131).  Epilogue arithmetic restates
 // codegen.py:1204-1244 (fp32 on the accumulator, then cast).
 //
-// Persistent, warp-specialised CTA (192 threads), one 128 x 256 accumulator tile at a time:
+// Persistent, warp-specialised CTA (320 threads), one 128 x 256 accumulator tile at a time:
 //   warp 0     TMA producer: a 4-deep ring of {A 128x64, B 256x64} stages behind mbarriers
-//   warp 1     MMA issuer: one thread, tcgen05.mma M=128 N=256 K=16, fp32 accumulators in
+//   warp 1     MMA issuer: warp-uniform loop, one elected lane issues tcgen05.mma M=128 N=256 K=16, fp32 accumulators in
 //              TMEM, two accumulator buffers (2 x 256 columns) so the epilogue of tile t
 //              overlaps the main loop of tile t+1
-//   warps 2-5  epilogue: TMEM -> registers -> epilogue math -> 16-byte global stores
+//   warps 2-9  epilogue, two warpgroups: a thread owns one row and half of the tile's columns;
+//              TMEM -> registers -> epilogue math -> 16-byte global stores
 //
 // Epilogue classes:
 //   PLAIN   row_scale, bias, unary activation, residual              (256 output columns / tile)
