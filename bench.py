@@ -301,7 +301,10 @@ def run_ours(args):
         ops.fa_fwd(q, k, v, causal=causal, out=out)
         b.record()
     torch.cuda.synchronize()
-    launch_ms_bracketed = statistics.median(a.elapsed_time(b) for a, b in evs)
+    per_launch = sorted(a.elapsed_time(b) for a, b in evs)
+    launch_ms_bracketed = statistics.median(per_launch)
+    launch_stats = {"median": launch_ms_bracketed, "min": per_launch[0], "p90": per_launch[int(0.9 * (len(per_launch) - 1))],
+                    "launches": len(per_launch)}
     # Only this kernel launches inside the timed region, back to back on one stream, so its average
     # launch duration is the region's device time over its launches (events around every single
     # launch add the gap between an event and the next launch; that figure is kept beside it).
@@ -328,7 +331,7 @@ def run_ours(args):
                 "peak_kind": f"{'sustained (power-capped clocks during the timed region)' if sustained_run else 'burst'}"
                              f" dense bf16, of {peaks['source']}",
                 "frac_of_burst_peak": achieved / peaks["burst"], "frac_of_sustained_peak": achieved / peaks["sustained"],
-                "launch_ms": launch_ms, "launch_ms_events_around_each_launch": launch_ms_bracketed}
+                "launch_ms": launch_ms, "launch_ms_events_around_each_launch": launch_stats}
 
     # ---- the same launch in a long back-to-back loop ----------------------------------------
     # A 1 kW part drops its SM clock under the power cap after a few hundred milliseconds of this

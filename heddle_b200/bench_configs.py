@@ -64,6 +64,17 @@ def main() -> None:
         ms = _time(lambda: ops.fa_fwd(qq, kq, vq, causal=False, scales=sc), args.steps, args.warmup)
         flops = 4.0 * B * H * S * S * D
         line.update(workload="fp8_e4m3_noncausal_B4_H32_S8192_D128", dtype="e4m3")
+        # an FP8 tensor-core reference measured in the same run (no FP8 peak is on file): cuBLASLt
+        # e4m3 x e4m3 -> bf16 at 8192^3 through torch._scaled_mm
+        try:
+            n = 8192
+            a8 = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn)
+            b8 = torch.randn(n, n, device="cuda").to(torch.float8_e4m3fn).t()
+            one = torch.ones((), device="cuda")
+            mm_ms = _time(lambda: torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16), 20, 5)
+            line.update(fp8_gemm_reference_tflops=2.0 * n ** 3 / mm_ms / 1e9)
+        except Exception as exc:  # the reference is informative only
+            line.update(fp8_gemm_reference_tflops=None, fp8_gemm_reference_error=str(exc)[:80])
     elif args.config == "h2o":
         B, H, S, D = 4, 32, 4096, 128
         q, k, v = rnd(B, H, S, D).bfloat16(), rnd(B, H, S, D).bfloat16(), rnd(B, H, S, D).bfloat16()
@@ -153,6 +164,8 @@ def main() -> None:
         line.update(workload="llama_layer_h4096_heads32_inter11008_B8_S2048", dtype="bf16", eager_pytorch_ms=eager_ms,
                     eager_pytorch_tflops=flops / eager_ms / 1e9)
     line.update(ms=ms, value=flops / ms / 1e9, algorithmic_tflop=flops / 1e12, device_status_word=ops.status_word())
+    if line.get("fp8_gemm_reference_tflops"):
+        line.update(frac_of_fp8_gemm_reference=line["value"] / line["fp8_gemm_reference_tflops"])
     print(json.dumps(line), flush=True)
 
 
