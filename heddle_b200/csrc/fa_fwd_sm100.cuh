@@ -236,7 +236,12 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<T, D, 
         // (half the FMA-pipe instructions), the exponentials on the MUFU, one per score.
         float sum0, sum1, sum2, sum3;
         {
-          const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_scaled, -m_scaled);
+          // FP8: P is stored as p * kPScale; the power of two is added to the exponent instead of
+          // multiplying each value, so the sums below are kPScale times the row sum (divided out
+          // once, when the block's row sum is published)
+          constexpr float kPShift = FaTraits<T>::kFp8 ? 5.0f : 0.0f;
+          static_assert(!FaTraits<T>::kFp8 || FaTraits<T>::kPScale == 32.0f, "kPShift is log2(kPScale)");
+          const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(kPShift - m_scaled, kPShift - m_scaled);
           uint64_t sa = pack_f32x2(0.f, 0.f), sb = pack_f32x2(0.f, 0.f);
           constexpr int kChunk = FaTraits<T>::kFp8 ? 64 : 32;  // scores per 16 packed TMEM columns
 #pragma unroll
@@ -263,9 +268,8 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<T, D, 
               sa = add_f32x2(sa, pack_f32x2(a0, a1));
               sb = add_f32x2(sb, pack_f32x2(b0, b1));
               if constexpr (FaTraits<T>::kFp8) {
-                // e4m3 P: four values per TMEM column, scaled by kPScale (a power of two, exact)
-                constexpr float ps = FaTraits<T>::kPScale;
-                pk[e / 4] = pack4_e4m3(a0 * ps, a1 * ps, b0 * ps, b1 * ps);
+                // e4m3 P: four values per TMEM column (already scaled by kPScale)
+                pk[e / 4] = pack4_e4m3(a0, a1, b0, b1);
               } else {
                 pk[e / 2] = Pack2<T>::pack(a0, a1);
                 pk[e / 2 + 1] = Pack2<T>::pack(b0, b1);
@@ -291,7 +295,7 @@ __device__ __forceinline__ void fa_softmax_role(const FaParams& p, FaSmem<T, D, 
       // consumed first: the correction warpgroup arrives on p_full after reading it (and, for a
       // one-step block, after the previous block's epilogue read this slot).
       if (!mbar_wait_warp(&s.p_full[i], (p_cnt & 1) ^ 1, ctx, kRoleSoftmax)) return;
-      s.alpha[i][row] = l;
+      s.alpha[i][row] = l * (1.0f / FaTraits<T>::kPScale);
       s.stat_m[i][row] = m;
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.corr_full[i]);
