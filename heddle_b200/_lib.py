@@ -86,7 +86,7 @@ class PrepareArgs(C.Structure):
 
 # every symbol include/heddle_b200.h declares
 EXPORTS = (
-    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_status_word",
+    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_status_word",
     "hb_version",
     "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma",
 )
@@ -118,6 +118,9 @@ def load() -> C.CDLL:
     lib.hb_rms_rowstat.restype = C.c_int
     lib.hb_prepare_weight.argtypes = [C.POINTER(PrepareArgs)]
     lib.hb_prepare_weight.restype = C.c_int
+    lib.hb_row_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_float,
+                                   C.c_int32, C.c_void_p]
+    lib.hb_row_softmax.restype = C.c_int
     lib.hb_status_word.argtypes = [C.POINTER(C.c_uint32)]
     lib.hb_status_word.restype = C.c_int
     lib.hb_version.argtypes = []

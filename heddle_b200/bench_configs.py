@@ -1,6 +1,6 @@
 """Device-resident timings of the secondary configurations (one JSON line each):
 
-    python -m heddle_b200.bench_configs --config c3|c4|c5|gemm|h2o|rowstat [--steps N] [--warmup W]
+    python -m heddle_b200.bench_configs --config c3|c4|c5|gemm|h2o|rowstat|softmax [--steps N] [--warmup W]
 
   c3    BF16 causal GQA, one GPU's share of B=8 Hq=64 Hkv=8 S=8192 D=128 at 8 GPUs
         (one KV head with its 8 query heads, all 8 batches)
@@ -9,6 +9,7 @@
         hidden 4096, 32 x 128 heads, SwiGLU 11008, B=8 S=2048, bf16
   gemm  the layer's gate/up projection as one SwiGLU GEMM: M=16384 N=2x11008 K=4096
   h2o   H2O score on the headline attention shape (B=4 H=32 S=4096 D=128, causal)
+  softmax  row softmax of a 32768 x 4096 bf16 score matrix (HBM-bound, GB/s of algorithmic bytes)
   rowstat  RMSNorm row statistic fused with the residual add on the layer's activations
         (16384 x 4096 bf16): HBM-bound, reported in GB/s of algorithmic bytes
 
@@ -38,7 +39,7 @@ def _time(fn, steps: int, warmup: int) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", choices=["c3", "c4", "c5", "gemm", "h2o", "rowstat"], required=True)
+    ap.add_argument("--config", choices=["c3", "c4", "c5", "gemm", "h2o", "rowstat", "softmax"], required=True)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -82,6 +83,22 @@ def main() -> None:
         ms = _time(lambda: ops.h2o_score(q, k, lse, causal=True), args.steps, args.warmup)
         flops = 1.0 * B * H * S * S * D  # one causal Q K^T product
         line.update(workload="h2o_score_bf16_causal_B4_H32_S4096_D128", dtype="bf16")
+    elif args.config == "softmax":
+        R, Cn = 32768, 4096
+        xs = [rnd(R, Cn).bfloat16() for _ in range(3)]  # 3 x 268 MB in rotation: no launch finds its input in L2
+        it = [0]
+
+        def run():
+            i = it[0] = (it[0] + 1) % 3
+            ops.row_softmax(xs[i], 0.125)
+
+        ms = _time(run, args.steps, args.warmup)
+        nbytes = 2.0 * R * Cn * 2
+        torch_ms = _time(lambda: torch.softmax(xs[0] * 0.125, dim=-1), args.steps, args.warmup)
+        line.update(workload="row_softmax_R32768_C4096", dtype="bf16", unit="GB/s", ms=ms, value=nbytes / ms / 1e6,
+                    algorithmic_mb=nbytes / 1e6, torch_mul_softmax_ms=torch_ms, device_status_word=ops.status_word())
+        print(json.dumps(line), flush=True)
+        return
     elif args.config == "rowstat":
         M, N = 16384, 4096
         # several activation buffers in rotation so that no launch finds its input in L2 (126 MB)

@@ -102,6 +102,12 @@ def hb_rms_rowstat(x, eps):
     return ops.rms_rowstat(x, None, eps)[1]
 
 
+@torch.fx.wrap
+def hb_softmax(x, scale=1.0):
+    """softmax(scale * x) over the last dimension in one kernel (``hb_row_softmax``)."""
+    return ops.row_softmax(x, scale)
+
+
 GEMM_LEAVES = (hb_linear, hb_swiglu, hb_linear_multi)
 
 
@@ -468,6 +474,58 @@ def _pass_merge_siblings(gm: fx.GraphModule) -> int:
     return merged
 
 
+def _softmax_dim(n: fx.Node):
+    """(input, dim, has_dtype) of a softmax node, or None."""
+    name = _fname(n)
+    if name != "softmax" or n.op not in ("call_function", "call_method"):
+        return None
+    args = list(n.args)
+    x = args[0] if args else n.kwargs.get("input")
+    dim = args[1] if len(args) > 1 else n.kwargs.get("dim")
+    has_dtype = (len(args) > 2 and args[-1] is not None) or n.kwargs.get("dtype") is not None
+    if n.op == "call_function" and len(args) > 3:  # F.softmax(input, dim, _stacklevel, dtype)
+        has_dtype = args[3] is not None
+    return x, dim, has_dtype
+
+
+def _pass_softmax(gm: fx.GraphModule) -> int:
+    """softmax over the last axis of a 16-bit tensor (what remains of attention the rewrites could
+    not take, e.g. with an arbitrary mask) -> hb_softmax; a scalar multiply or divide that only
+    feeds the softmax is folded into its scale.  The reference compiles such reductions with its
+    generated softmax-like kernel (codegen.py:1246-1400)."""
+    done = 0
+    for n in list(gm.graph.nodes):
+        m = _softmax_dim(n)
+        if m is None:
+            continue
+        x, dim, has_dtype = m
+        shp = _meta_shape(x)
+        if has_dtype or not isinstance(x, fx.Node) or shp is None or not isinstance(dim, int):
+            continue
+        if dim not in (-1, len(shp) - 1) or _meta_dtype(x) not in (torch.bfloat16, torch.float16):
+            continue
+        if shp[-1] % 8 != 0 or shp[-1] > 16384:
+            continue
+        scale, src = 1.0, x
+        if _fname(x) in ("mul", "truediv", "div") and len(x.users) == 1 and len(x.args) == 2:
+            a, b = x.args
+            if isinstance(a, fx.Node) and isinstance(b, (int, float)) and b != 0:
+                scale, src = (float(b) if _fname(x) == "mul" else 1.0 / float(b)), a
+            elif _fname(x) == "mul" and isinstance(b, fx.Node) and isinstance(a, (int, float)):
+                scale, src = float(a), b
+        if src is not x and (_meta_dtype(src) != _meta_dtype(x) or _meta_shape(src) != shp):
+            scale, src = 1.0, x
+        with gm.graph.inserting_before(n):
+            new = gm.graph.call_function(hb_softmax, (src, scale))
+        new.meta = dict(n.meta)
+        n.replace_all_uses_with(new)
+        gm.graph.erase_node(n)
+        done += 1
+    if done:
+        gm.graph.eliminate_dead_code()
+    return done
+
+
 def fuse_gemm_epilogues(gm: fx.GraphModule) -> int:
     """Run all passes; returns the number of GEMM leaves in the rewritten graph."""
     _pass_rmsnorm(gm)
@@ -477,6 +535,7 @@ def fuse_gemm_epilogues(gm: fx.GraphModule) -> int:
     _pass_fold_rmsnorm(gm)
     _pass_rope(gm)
     _pass_merge_siblings(gm)
+    _pass_softmax(gm)
     gm.graph.lint()
     gm.recompile()
     return sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target in GEMM_LEAVES)

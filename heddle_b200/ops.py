@@ -244,6 +244,21 @@ def prepare_weight(weights: "Sequence[torch.Tensor]", gamma: Optional[torch.Tens
     return out
 
 
+def row_softmax(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """softmax(scale * x) over the last dimension (``hb_row_softmax``): bf16 / fp16, last dimension a
+    multiple of 8 and at most 16384."""
+    _require_cuda(x)
+    cols = x.shape[-1]
+    x2 = x.reshape(-1, cols)
+    if x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) % 8 != 0) or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    y = torch.empty((x2.shape[0], cols), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().hb_row_softmax(x2.data_ptr(), y.data_ptr(), x2.shape[0], cols, max(x2.stride(0), cols),
+                                              cols, float(scale), _DTYPES[x.dtype], _stream_ptr(x.device)))
+    return y.reshape(x.shape)
+
+
 def h2o_score(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, causal: bool = True,
               softmax_scale: Optional[float] = None, layout: str = "bhsd") -> torch.Tensor:
     """H2O score through ``hb_h2o_score``: score[b,h,j] = sum_i exp(s_ij - lse_i), fp32 [B, Hq, Skv].

@@ -227,6 +227,15 @@ typedef struct hb_prepare_args {
 
 int hb_prepare_weight(const hb_prepare_args* args);
 
+/*
+ * y = softmax(scale * x) over the last axis of a [rows, cols] matrix (bf16 / fp16, fp32 math,
+ * cols a multiple of 8 and at most 16384).  The native counterpart of the reference's generated
+ * softmax-like reduction kernel (Heddle/heddle/frontend/codegen.py:1246-1400: one 32-thread CTA
+ * per row, exp2 with log2(e), block-wise online merge); here a row is read and written once.
+ */
+int hb_row_softmax(const void* x, void* y, int64_t rows, int32_t cols, int64_t ld_x, int64_t ld_y,
+                   float scale, int32_t dtype, void* stream);
+
 /* Device-side status word of the current device (0 = no bounded wait ever gave up);
  * reading it synchronises the device. */
 int hb_status_word(uint32_t* out);

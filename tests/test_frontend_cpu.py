@@ -216,3 +216,34 @@ def test_llama_layer_lowering():
     assert sw.kwargs.get("row_scale") is not None and sw.kwargs.get("gamma") is not None
     sd = next(n for n in gm.graph.nodes if n.target is B._tilelang_sdpa_direct)
     assert sd.kwargs["is_causal"] is True and sd.kwargs.get("out_bshd") is True
+
+
+def test_leftover_softmax_is_lowered_with_its_scale():
+    """Attention with a mask the rewrites refuse keeps its softmax; a 16-bit softmax over the last
+    axis becomes hb_softmax and the scalar scale in front of it is folded in."""
+    class M(torch.nn.Module):
+        def forward(self, q, k, v):
+            s = torch.matmul(q, k.transpose(-2, -1))
+            p = torch.softmax(s * 0.125, dim=-1)
+            return torch.matmul(p, v)
+
+    q, k, v = qkv(dtype=torch.bfloat16)
+    # an arbitrary additive bias in front keeps the attention rewrite away in the second module
+    class M2(torch.nn.Module):
+        def forward(self, q, k, v, bias):
+            s = torch.matmul(q, k.transpose(-2, -1)) / 8.0 + bias
+            return torch.matmul(F.softmax(s, dim=-1), v)
+
+    gm = capture(M2(), q, k, v, torch.randn(64, 64).to(torch.bfloat16))
+    leaves = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is fusion.hb_softmax]
+    assert len(leaves) == 1 and leaves[0].args[1] == 1.0  # the scale sits before the bias: not foldable
+    assert not any(getattr(t, "__name__", "") == "softmax" for t in targets(gm))
+
+    class M3(torch.nn.Module):
+        def forward(self, x):
+            return (x / 4.0).softmax(-1) + torch.softmax(x, dim=1) + F.softmax(x.float(), dim=-1).to(x.dtype)
+
+    gm = capture(M3(), torch.randn(4, 32, 64).to(torch.float16))
+    leaves = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is fusion.hb_softmax]
+    # only the last-axis, 16-bit one is taken (with its 1/4 folded); dim=1 and fp32 stay in PyTorch
+    assert len(leaves) == 1 and leaves[0].args[1] == 0.25

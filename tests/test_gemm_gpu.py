@@ -150,3 +150,27 @@ def test_prepare_weight_stacks_and_folds(ops):
     y = ops.gemm_epilogue(x, ops.prepare_weight(w3, gam), "none")
     ref = x.float() @ (torch.cat(w3, 0).float() * gam.float()[None, :]).to(torch.bfloat16).float().t()
     assert (y.float() - ref).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("rows,cols,dtype", [
+    (37, 64, torch.bfloat16), (300, 2048, torch.float16), (64, 4096, torch.bfloat16), (9, 16384, torch.bfloat16),
+    (5, 200, torch.float16),
+])
+def test_row_softmax(ops, rows, cols, dtype):
+    """hb_row_softmax against torch.softmax in fp32 on the CPU (one rounding to the 16-bit type)."""
+    g = torch.Generator().manual_seed(rows + cols)
+    x = (3.0 * torch.randn(rows, cols, generator=g)).to(dtype)
+    masked = x.clone()
+    masked[0, : cols // 2] = float("-inf")  # masked entries (meaningful for a positive scale only)
+    for scale in (1.0, 0.125, -0.5):
+        xin = masked if scale > 0 else x
+        y = ops.row_softmax(xin.cuda(), scale)
+        ref = torch.softmax(xin.float() * scale, dim=-1)
+        assert y.dtype == dtype and y.shape == x.shape
+        assert (y.float().cpu() - ref).abs().max().item() <= 4e-3
+        assert (y.float().sum(-1).cpu() - 1.0).abs().max().item() <= 1e-2
+    x3 = (torch.randn(2, 3, 40, 72, generator=g)).to(dtype)
+    y3 = ops.row_softmax(x3.cuda())
+    assert (y3.float().cpu() - torch.softmax(x3.float(), -1)).abs().max().item() <= 4e-3
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        ops.row_softmax(torch.zeros(4, 12, dtype=dtype, device="cuda"))
