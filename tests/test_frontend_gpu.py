@@ -110,3 +110,31 @@ def test_full_size_llama_layer(backend):
 def copy_to_cuda(module):
     import copy
     return copy.deepcopy(module).cuda()
+
+
+def test_biased_attention_runs_the_softmax_kernel(backend):
+    """An additive bias the attention rewrites refuse: the graph keeps its matmuls and gets
+    hb_softmax for the row softmax; result against the same module in fp32 on the CPU."""
+    from heddle_b200.frontend import fusion
+
+    class Biased(torch.nn.Module):
+        def forward(self, q, k, v, bias):
+            s = torch.matmul(q, k.transpose(-2, -1)) / 8.0 + bias
+            return torch.matmul(torch.softmax(s, dim=-1), v)
+
+    g = torch.Generator().manual_seed(4)
+    q, k, v = (torch.randn(2, 4, 256, 64, generator=g).to(torch.bfloat16) for _ in range(3))
+    bias = torch.randn(256, 256, generator=g).to(torch.bfloat16)
+    seen = []
+
+    def recording(gm, example_inputs):
+        out = backend(gm, example_inputs)
+        seen.append([n.target for n in out.graph.nodes if n.op == "call_function"] if hasattr(out, "graph") else [])
+        return out
+
+    torch._dynamo.reset()
+    with torch.no_grad():
+        got = torch.compile(Biased(), backend=recording)(q.cuda(), k.cuda(), v.cuda(), bias.cuda())
+        ref = Biased()(q.float(), k.float(), v.float(), bias.float())
+    assert any(fusion.hb_softmax in t for t in seen)
+    assert (got.float().cpu() - ref).abs().max().item() <= 3e-2
