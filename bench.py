@@ -412,8 +412,9 @@ def run_ours(args):
         e2e_ms = max_over_ranks(start.elapsed_time(stop)) / e2e_steps
         h2d = 3 * q.numel() * q.element_size()
         d2h = ho.numel() * ho.element_size() + hl.numel() * 4
-        e2e = {"value": flops_rank * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+        # bytes of the whole job per step (every rank moves its own shard), like `value`
+        e2e = {"value": flops_rank * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+               "d2h_bytes_per_step": d2h * world, "bytes_per_rank": {"h2d": h2d, "d2h": d2h}, "ms_per_step": e2e_ms,
                "how": "ops.fa_fwd per batch element, pinned host buffers, H2D / kernel / D2H on three streams"}
 
     # ---- CPU baseline (rank 0, N = 1 only) -------------------------------------------------
