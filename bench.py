@@ -142,9 +142,10 @@ def use_all_host_threads() -> int:
     return torch.get_num_threads()
 
 
-def cpu_slice_tflops(heads: int = 2, reps: int = 3):
+def cpu_slice_tflops(heads: int = 8, reps: int = 31):
     """Reference eager fp32 attention on the host cores for a slice of the workload:
-    one batch element x ``heads`` query heads at full sequence length."""
+    one batch element x ``heads`` query heads at full sequence length, repeated until about ten
+    seconds of CPU work are sampled (median reported)."""
     from oracle import attention_oracle as O
 
     use_all_host_threads()
