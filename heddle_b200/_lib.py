@@ -88,7 +88,7 @@ class PrepareArgs(C.Structure):
 EXPORTS = (
     "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_status_word",
     "hb_version",
-    "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma",
+    "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma", "hb_debug_wait_timeout",
 )
 
 _lib = None
@@ -133,6 +133,8 @@ def load() -> C.CDLL:
     lib.hb_shutdown.restype = C.c_int
     lib.hb_debug_umma.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     lib.hb_debug_umma.restype = C.c_int
+    lib.hb_debug_wait_timeout.argtypes = [C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]
+    lib.hb_debug_wait_timeout.restype = C.c_int
     _lib = lib
     return lib
 

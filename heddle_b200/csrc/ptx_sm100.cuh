@@ -134,12 +134,13 @@ enum : uint32_t {
   kStatusSmemMisaligned = 0x200,
 };
 
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait, far above any real latency
+
 struct AbortCtx {
   volatile uint32_t* cta_flag;  // shared memory, one per CTA
   uint32_t* status;             // global memory, one per device
+  uint64_t limit_ns = kWaitLimitNs;  // the time-out probe sets a short one
 };
-
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait, far above any real latency
 
 __device__ __forceinline__ void raise_abort(const AbortCtx& ctx, uint32_t code) {
   *ctx.cta_flag = 1u;
@@ -194,7 +195,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > ctx.limit_ns) {
         raise_abort(ctx, kStatusWaitTimeout | role);
         return false;
       }

@@ -98,6 +98,16 @@ def status_word() -> int:
     return int(w.value)
 
 
+def debug_wait_timeout(limit_us: int = 200):
+    """Run the bounded-wait probe (``hb_debug_wait_timeout``): returns (status code, [ok0, ns0, ok1, ns1])."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("heddle_b200 kernels need a CUDA device: there is no CPU fallback")
+    status = C.c_uint32(0)
+    res = (C.c_uint64 * 4)()
+    _lib.check(_lib.load().hb_debug_wait_timeout(int(limit_us), C.byref(status), res))
+    return int(status.value), [int(v) for v in res]
+
+
 def debug_umma(mode: int, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """One tcgen05 tile through the library's descriptor helpers (see hb_debug_umma)."""
     _require_cuda(a, b)

@@ -257,6 +257,16 @@ int hb_shutdown(void);
 int hb_debug_umma(int mode, const void* a, const void* b, float* out, int32_t kn, int32_t dtype,
                   void* stream);
 
+/*
+ * Failure-detection probe: one small CTA waits on a barrier that is never signalled, with a
+ * limit of limit_us microseconds (1..100000).  The wait gives up, raises the CTA's abort flag and
+ * records kStatusWaitTimeout | role (0x170) in a scratch status word, a second warp leaves its own
+ * wait on seeing the flag, the kernel ends normally.  status_out receives the code; result4 =
+ * {warp 0 returned ok?, its wait in ns, warp 1 returned ok?, its wait in ns}.  Nothing faults or
+ * hangs; the device status word read by hb_status_word is not touched.
+ */
+int hb_debug_wait_timeout(uint32_t limit_us, uint32_t* status_out, uint64_t* result4);
+
 #ifdef __cplusplus
 }
 #endif
