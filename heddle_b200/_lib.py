@@ -62,6 +62,23 @@ class H2oArgs(C.Structure):
     ]
 
 
+class FaBwdArgs(C.Structure):
+    """Mirror of hb_fa_bwd_args."""
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("d_o", C.c_void_p),
+        ("lse", C.c_void_p), ("delta", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Sq", C.c_int32), ("Skv", C.c_int32),
+        ("D", C.c_int32),
+        ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64), ("q_stride_s", C.c_int64),
+        ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64), ("k_stride_s", C.c_int64),
+        ("v_stride_b", C.c_int64), ("v_stride_h", C.c_int64), ("v_stride_s", C.c_int64),
+        ("o_stride_b", C.c_int64), ("o_stride_h", C.c_int64), ("o_stride_s", C.c_int64),
+        ("do_stride_b", C.c_int64), ("do_stride_h", C.c_int64), ("do_stride_s", C.c_int64),
+        ("causal", C.c_int32), ("softmax_scale", C.c_float), ("dtype", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
 class GemmArgs(C.Structure):
     _fields_ = [
         ("a", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p),
@@ -86,7 +103,7 @@ class PrepareArgs(C.Structure):
 
 # every symbol include/heddle_b200.h declares
 EXPORTS = (
-    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_status_word",
+    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_status_word",
     "hb_version",
     "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma", "hb_debug_wait_timeout",
 )
@@ -109,6 +126,9 @@ def load() -> C.CDLL:
     lib.hb_fa_fwd.restype = C.c_int
     lib.hb_fa_fwd_noalloc.argtypes = [C.POINTER(FaArgs)]
     lib.hb_fa_fwd_noalloc.restype = C.c_int
+    for name in ("hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq"):
+        getattr(lib, name).argtypes = [C.POINTER(FaBwdArgs)]
+        getattr(lib, name).restype = C.c_int
     lib.hb_h2o_score.argtypes = [C.POINTER(H2oArgs)]
     lib.hb_h2o_score.restype = C.c_int
     lib.hb_gemm_epilogue.argtypes = [C.POINTER(GemmArgs)]

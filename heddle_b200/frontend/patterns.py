@@ -1,7 +1,8 @@
 """Attention patterns and their replacements — counterpart of Heddle/heddle/frontend/patterns.py.
 
 Kept from the reference: the BSHD pattern function (patterns.py:134-144), the
-``torch.autograd.Function`` wrappers (forward only, :146-191, :215-257), the
+``torch.autograd.Function`` wrappers (:146-191, :215-257; forward only in the reference, the
+flash-attention one has a backward here), the
 ``@torch.fx.wrap`` leaf callables that end up as single ``call_function`` nodes, and
 ``_heuristic_config`` (:22) which now returns the one fixed sm_100a schedule instead of
 ranking candidates with CP-SAT / ptxas feedback.
@@ -45,11 +46,27 @@ def scaled_dot_product_attention_pattern(q, k, v, scale):
 
 
 class TileLangFlashAttnFunc(torch.autograd.Function):
-    """(B, S, H, D) in and out, non-causal, forward only (patterns.py:146-191)."""
+    """(B, S, H, D) in and out, non-causal (patterns.py:146-191).
+
+    The reference's Function is forward only; its backward is sketched as the separated
+    preprocess / dK,dV / dQ kernels (bwd_separator.py:366-455, with ``backward`` saving
+    Q, K, V, O, LSE at :399-405).  That split is what ``backward`` runs here: when a gradient is
+    needed the forward keeps the LSE, and head_dim 128 in bf16 / fp16 is required."""
 
     @staticmethod
     def forward(ctx, q, k, v, scale=None):
+        ctx.scale = scale
+        if any(ctx.needs_input_grad[:3]):
+            out, lse = ops.fa_fwd(q, k, v, causal=False, softmax_scale=scale, layout="bshd", return_lse=True)
+            ctx.save_for_backward(q, k, v, out, lse)
+            return out
         return ops.fa_fwd(q, k, v, causal=False, softmax_scale=scale, layout="bshd")
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = ops.fa_bwd(q, k, v, out, grad_out, lse, causal=False, softmax_scale=ctx.scale, layout="bshd")
+        return dq, dk, dv, None
 
     @staticmethod
     def symbolic(g, q, k, v, scale=None):

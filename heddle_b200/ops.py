@@ -91,6 +91,96 @@ def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = 
     return (out, lse) if return_lse else out
 
 
+def _bwd_args(q, k, v, o, d_o, lse, delta, causal, softmax_scale, layout):
+    """Validated ``hb_fa_bwd_args`` for tensors in ``layout``; returns (args, kept-alive tensors, dims)."""
+    _require_cuda(q, k, v, o, d_o, lse, delta)
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"attention backward supports bf16 and fp16, got {q.dtype}")
+    for name, t in (("k", k), ("v", v), ("o", o), ("d_o", d_o)):
+        if t is not None and t.dtype != q.dtype:
+            raise TypeError(f"{name} has dtype {t.dtype}, q has {q.dtype}")
+    if layout == "bhsd":
+        b_ax, h_ax, s_ax = 0, 1, 2
+    elif layout == "bshd":
+        b_ax, h_ax, s_ax = 0, 2, 1
+    else:
+        raise ValueError(f"unknown layout {layout!r}")
+    q, k, v, d_o = (_inner_contiguous(t) for t in (q, k, v, d_o))
+    o = _inner_contiguous(o) if o is not None else None
+    B, Hq, Sq, D = q.shape[b_ax], q.shape[h_ax], q.shape[s_ax], q.shape[3]
+    Hkv, Skv = k.shape[h_ax], k.shape[s_ax]
+    if k.shape[b_ax] != B or v.shape != k.shape or k.shape[3] != D or d_o.shape != q.shape or (
+            o is not None and o.shape != q.shape):
+        raise ValueError("shape mismatch between q, k, v, o and d_o")
+    keep = [q, k, v, d_o, o]
+    a = _lib.FaBwdArgs()
+    a.q, a.k, a.v, a.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr()
+    a.o = o.data_ptr() if o is not None else None
+    for name, t in (("lse", lse), ("delta", delta)):
+        if t is not None:
+            if t.dtype != torch.float32 or tuple(t.shape) != (B, Hq, Sq) or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous fp32 [B, Hq, Sq] = {(B, Hq, Sq)} tensor")
+            setattr(a, name, t.data_ptr())
+    a.B, a.Hq, a.Hkv, a.Sq, a.Skv, a.D = B, Hq, Hkv, Sq, Skv, D
+    a.q_stride_b, a.q_stride_h, a.q_stride_s = q.stride(b_ax), q.stride(h_ax), q.stride(s_ax)
+    a.k_stride_b, a.k_stride_h, a.k_stride_s = k.stride(b_ax), k.stride(h_ax), k.stride(s_ax)
+    a.v_stride_b, a.v_stride_h, a.v_stride_s = v.stride(b_ax), v.stride(h_ax), v.stride(s_ax)
+    a.do_stride_b, a.do_stride_h, a.do_stride_s = d_o.stride(b_ax), d_o.stride(h_ax), d_o.stride(s_ax)
+    if o is not None:
+        a.o_stride_b, a.o_stride_h, a.o_stride_s = o.stride(b_ax), o.stride(h_ax), o.stride(s_ax)
+    a.causal = 1 if causal else 0
+    a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    a.dtype = _DTYPES[q.dtype]
+    a.stream = _stream_ptr(q.device)
+    return a, keep, (B, Hq, Hkv, Sq, Skv, D)
+
+
+def fa_bwd_preprocess(o: torch.Tensor, d_o: torch.Tensor, *, layout: str = "bhsd") -> torch.Tensor:
+    """delta[b,h,q] = sum_d O * dO through ``hb_fa_bwd_preprocess``; fp32 [B, H, Sq]."""
+    b_ax, h_ax, s_ax = (0, 1, 2) if layout == "bhsd" else (0, 2, 1)
+    delta = torch.empty((o.shape[b_ax], o.shape[h_ax], o.shape[s_ax]), dtype=torch.float32, device=o.device)
+    a, keep, _ = _bwd_args(o, o, o, o, d_o, None, delta, False, None, layout)
+    with torch.cuda.device(o.device):
+        _lib.check(_lib.load().hb_fa_bwd_preprocess(C.byref(a)))
+    return delta
+
+
+def fa_bwd_dkdv(q, k, v, d_o, lse, delta, *, causal: bool = False, softmax_scale: Optional[float] = None,
+                layout: str = "bhsd") -> Tuple[torch.Tensor, torch.Tensor]:
+    """dK, dV through ``hb_fa_bwd_dkdv``; contiguous [B, Hkv, Skv, D] (a transposed view for "bshd")."""
+    a, keep, (B, Hq, Hkv, Sq, Skv, D) = _bwd_args(q, k, v, None, d_o, lse, delta, causal, softmax_scale, layout)
+    dk = torch.empty((B, Hkv, Skv, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty_like(dk)
+    a.dk, a.dv = dk.data_ptr(), dv.data_ptr()
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().hb_fa_bwd_dkdv(C.byref(a)))
+    return (dk, dv) if layout == "bhsd" else (dk.transpose(1, 2), dv.transpose(1, 2))
+
+
+def fa_bwd_dq(q, k, v, d_o, lse, delta, *, causal: bool = False, softmax_scale: Optional[float] = None,
+              layout: str = "bhsd") -> torch.Tensor:
+    """dQ through ``hb_fa_bwd_dq``; contiguous [B, Hq, Sq, D] (a transposed view for "bshd")."""
+    a, keep, (B, Hq, Hkv, Sq, Skv, D) = _bwd_args(q, k, v, None, d_o, lse, delta, causal, softmax_scale, layout)
+    dq = torch.empty((B, Hq, Sq, D), dtype=q.dtype, device=q.device)
+    a.dq = dq.data_ptr()
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().hb_fa_bwd_dq(C.byref(a)))
+    return dq if layout == "bhsd" else dq.transpose(1, 2)
+
+
+def fa_bwd(q, k, v, o, d_o, lse, *, causal: bool = False, softmax_scale: Optional[float] = None,
+           layout: str = "bhsd") -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Attention backward as preprocess -> dK, dV -> dQ (the split of the reference's
+    ``create_separated_bwd_function``, Heddle/heddle/frontend/bwd_separator.py:366-455).
+
+    ``lse`` is the natural-log LSE [B, Hq, Sq] of the forward pass.  Returns (dQ, dK, dV)."""
+    lse = lse.to(torch.float32).contiguous()
+    delta = fa_bwd_preprocess(o, d_o, layout=layout)
+    dk, dv = fa_bwd_dkdv(q, k, v, d_o, lse, delta, causal=causal, softmax_scale=softmax_scale, layout=layout)
+    dq = fa_bwd_dq(q, k, v, d_o, lse, delta, causal=causal, softmax_scale=softmax_scale, layout=layout)
+    return dq, dk, dv
+
+
 def status_word() -> int:
     """Device status word of the current device: 0 unless a bounded device-side wait gave up."""
     w = C.c_uint32(0)

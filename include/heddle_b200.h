@@ -228,6 +228,51 @@ typedef struct hb_prepare_args {
 int hb_prepare_weight(const hb_prepare_args* args);
 
 /*
+ * Attention backward, split into three kernels with exclusive outputs (no atomic adds).  The
+ * reference sketches this interface and leaves the kernels unwritten:
+ *   Heddle/heddle/frontend/bwd_separator.py:366-455 (create_separated_bwd_function:
+ *     delta = preprocess(O, dO);  dK, dV = dkdv(Q, K, V, O, dO, LSE, delta);  dQ = dq(...))
+ *   delta[b,h,q] = sum_d O * dO
+ *   P = exp(scale * Q K^T + mask - LSE),  dP = dO V^T,  dS = P o (dP - delta)
+ *   dV = P^T dO,  dK = scale * dS^T Q,  dQ = scale * dS K
+ * q, d_o, o are [B, Hq, Sq, D] and k, v [B, Hkv, Skv, D] by element strides (head_dim contiguous,
+ * 16-byte aligned rows), lse is the natural-log LSE that hb_fa_fwd writes, lse and delta are
+ * [B, Hq, Sq] fp32 contiguous.  Outputs are contiguous: dq [B, Hq, Sq, D], dk and dv
+ * [B, Hkv, Skv, D] (with grouped queries a kv head's gradient is the sum over its query heads,
+ * formed inside the one CTA that owns the key tile).  bf16 / fp16, D = 128, causal mask aligned
+ * to the end of the keys (key <= query + Skv - Sq) as in hb_fa_fwd.
+ *   hb_fa_bwd_preprocess reads o, d_o            and writes delta
+ *   hb_fa_bwd_dkdv       reads q, k, v, d_o, lse, delta and writes dk, dv
+ *   hb_fa_bwd_dq         reads q, k, v, d_o, lse, delta and writes dq
+ */
+typedef struct hb_fa_bwd_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* lse;
+  float* delta;
+  void* dq;
+  void* dk;
+  void* dv;
+  int32_t B, Hq, Hkv, Sq, Skv, D;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  int64_t k_stride_b, k_stride_h, k_stride_s;
+  int64_t v_stride_b, v_stride_h, v_stride_s;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  int64_t do_stride_b, do_stride_h, do_stride_s;
+  int32_t causal;
+  float softmax_scale; /* <= 0 selects D^-1/2 */
+  int32_t dtype;       /* HB_BF16 or HB_FP16 */
+  void* stream;
+} hb_fa_bwd_args;
+
+int hb_fa_bwd_preprocess(const hb_fa_bwd_args* args);
+int hb_fa_bwd_dkdv(const hb_fa_bwd_args* args);
+int hb_fa_bwd_dq(const hb_fa_bwd_args* args);
+
+/*
  * y = softmax(scale * x) over the last axis of a [rows, cols] matrix (bf16 / fp16, fp32 math,
  * cols a multiple of 8 and at most 16384).  The native counterpart of the reference's generated
  * softmax-like reduction kernel (Heddle/heddle/frontend/codegen.py:1246-1400: one 32-thread CTA

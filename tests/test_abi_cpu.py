@@ -47,6 +47,8 @@ int main(void) {
   printf("%zu %zu\n", sizeof(hb_h2o_args), offsetof(hb_h2o_args, stream));
   printf("%zu %zu %zu %zu\n", sizeof(hb_prepare_args), offsetof(hb_prepare_args, ld_src), offsetof(hb_prepare_args, gamma),
          offsetof(hb_prepare_args, stream));
+  printf("%zu %zu %zu %zu %zu\n", sizeof(hb_fa_bwd_args), offsetof(hb_fa_bwd_args, B), offsetof(hb_fa_bwd_args, q_stride_b),
+         offsetof(hb_fa_bwd_args, causal), offsetof(hb_fa_bwd_args, stream));
   return 0;
 }'''
     with tempfile.TemporaryDirectory() as d:
@@ -65,6 +67,9 @@ int main(void) {
     pw = [int(x) for x in lines[3].split()]
     assert pw == [ctypes.sizeof(_lib.PrepareArgs), _lib.PrepareArgs.ld_src.offset, _lib.PrepareArgs.gamma.offset,
                   _lib.PrepareArgs.stream.offset]
+    bw = [int(x) for x in lines[4].split()]
+    assert bw == [ctypes.sizeof(_lib.FaBwdArgs), _lib.FaBwdArgs.B.offset, _lib.FaBwdArgs.q_stride_b.offset,
+                  _lib.FaBwdArgs.causal.offset, _lib.FaBwdArgs.stream.offset]
 
 
 def test_argument_validation_needs_no_gpu(built_lib):
@@ -90,6 +95,18 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_ERR_BAD_ARG  # null pointers
     a.Sq = 0
     assert built_lib.hb_fa_fwd(ctypes.byref(a)) == _lib.HB_OK  # empty problem is a no-op
+    for fn in (built_lib.hb_fa_bwd_preprocess, built_lib.hb_fa_bwd_dkdv, built_lib.hb_fa_bwd_dq):
+        assert fn(None) == _lib.HB_ERR_BAD_ARG
+        g = _lib.FaBwdArgs()
+        g.B, g.Hq, g.Hkv, g.Sq, g.Skv, g.D, g.dtype = 1, 4, 4, 128, 128, 64, _lib.HB_BF16
+        assert fn(ctypes.byref(g)) == _lib.HB_ERR_UNSUPPORTED  # head_dim 128 only
+        assert b"head_dim" in built_lib.hb_last_error()
+        g.D, g.dtype = 128, _lib.HB_FP8_E4M3
+        assert fn(ctypes.byref(g)) == _lib.HB_ERR_UNSUPPORTED  # 16-bit types only
+        g.dtype = _lib.HB_BF16
+        assert fn(ctypes.byref(g)) == _lib.HB_ERR_BAD_ARG  # null pointers
+        g.B = 0
+        assert fn(ctypes.byref(g)) == _lib.HB_OK  # empty problem is a no-op
     assert built_lib.hb_prepare_weight(None) == _lib.HB_ERR_BAD_ARG
     w = _lib.PrepareArgs()
     w.n_src, w.K, w.dtype = 5, 64, _lib.HB_BF16

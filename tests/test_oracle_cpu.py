@@ -117,3 +117,62 @@ def test_fp8_quant_roundtrip_bound():
     # e4m3 has 3 mantissa bits: relative error <= 2^-4 away from the subnormal range
     err = (O.dequantize_e4m3(xq, s) - x).abs()
     assert (err <= x.abs() * 2 ** -4 + s * 2 ** -9).all()
+
+
+@pytest.mark.parametrize("causal,Hq,Hkv,Sq,Skv", [(False, 2, 2, 48, 80), (True, 4, 2, 64, 64), (True, 2, 1, 40, 100)])
+def test_backward_restatement_matches_autograd(causal, Hq, Hkv, Sq, Skv):
+    """The closed-form split (delta, dS, dV, dK, dQ) equals torch.autograd on the eager graph."""
+    q, k, v = O.make_qkv(2, Hq, Hkv, Sq, Skv, 32, seed=11)
+    d_o = torch.randn(2, Hq, Sq, 32, generator=torch.Generator().manual_seed(12))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    out, _ = O.attention_eager(q, k, v, causal=causal)
+    gq, gk, gv = torch.autograd.grad(out, (q, k, v), d_o)
+    dq, dk, dv, delta = O.attention_backward(q.detach(), k.detach(), v.detach(), d_o, causal=causal)
+    torch.testing.assert_close(dq, gq, atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(dk, gk, atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(dv, gv, atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(delta, (out.detach() * d_o).sum(-1), atol=1e-5, rtol=1e-5)
+
+
+def test_bwd_separation_heuristic(monkeypatch):
+    """Decision rule and environment switches of the reference (bwd_separator.py:56-138)."""
+    from heddle_b200.frontend import bwd_separator as bs
+    for name in ("TILELANG_BWD_SEPARATION_MODE", "TILELANG_BWD_MIN_SEQ_FOR_SEP", "TILELANG_BWD_MIN_BATCH_HEADS"):
+        monkeypatch.delenv(name, raising=False)
+    assert bs.should_separate_bwd(4, 32, 4096, 128)
+    assert not bs.should_separate_bwd(4, 32, 512, 128)      # short sequence
+    assert not bs.should_separate_bwd(1, 2, 8192, 128)      # too little parallelism
+    assert bs.should_separate_bwd(1, 8, 2048, 128) and not bs.should_separate_bwd(1, 4, 2048, 128)
+    monkeypatch.setenv("TILELANG_BWD_SEPARATION_MODE", "unified")
+    assert not bs.should_separate_bwd(4, 32, 4096, 128)
+    monkeypatch.setenv("TILELANG_BWD_SEPARATION_MODE", "separated")
+    assert bs.should_separate_bwd(1, 1, 128, 128)
+    monkeypatch.setenv("TILELANG_BWD_SEPARATION_MODE", "auto")
+    monkeypatch.setenv("TILELANG_BWD_MIN_SEQ_FOR_SEP", "256")
+    assert bs.BWDSeparationConfig.from_env().min_seq_len_for_separation == 256
+    with pytest.raises(NotImplementedError):
+        bs.split_bwd_graph(None)
+
+
+def test_separated_bwd_function_order_and_arguments():
+    """create_separated_bwd_function calls preprocess -> dkdv -> dq with the reference's arguments."""
+    from heddle_b200.frontend import bwd_separator as bs
+    calls = []
+
+    def pre(B, H, T, D):
+        calls.append(("pre", B, H, T, D))
+        return lambda o, d_o: "delta"
+
+    def dkdv(B, H, Tq, Tkv, D, **kw):
+        calls.append(("dkdv", B, H, Tq, Tkv, D, kw["is_causal"], kw["block_M"], kw["block_N"]))
+        return lambda Q, K, V, O, dO, LSE, delta: ("dK", "dV") if delta == "delta" else None
+
+    def dq(B, H, Tq, Tkv, D, **kw):
+        calls.append(("dq", B, H, Tq, Tkv, D, kw["is_causal"], kw["block_M"], kw["block_N"]))
+        return lambda Q, K, V, O, dO, LSE, delta: "dQ"
+
+    f = bs.create_separated_bwd_function(pre, dkdv, dq)
+    Q = torch.zeros(2, 3, 16, 8)
+    K = torch.zeros(2, 3, 24, 8)
+    assert f(Q, K, K, Q, Q, None, is_causal=True, config=bs.BWDSeparationConfig()) == ("dQ", "dK", "dV")
+    assert calls == [("pre", 2, 3, 16, 8), ("dkdv", 2, 3, 16, 24, 8, True, 64, 128), ("dq", 2, 3, 16, 24, 8, True, 128, 64)]
