@@ -1,6 +1,6 @@
 """Device-resident timings of the secondary configurations (one JSON line each):
 
-    python -m heddle_b200.bench_configs --config c3|c4|c5|gemm|h2o|rowstat|softmax [--steps N] [--warmup W]
+    python -m heddle_b200.bench_configs --config c3|c4|c5|gemm|h2o|bwd|rowstat|softmax [--steps N] [--warmup W]
 
   c3    BF16 causal GQA, one GPU's share of B=8 Hq=64 Hkv=8 S=8192 D=128 at 8 GPUs
         (one KV head with its 8 query heads, all 8 batches)
@@ -9,6 +9,9 @@
         hidden 4096, 32 x 128 heads, SwiGLU 11008, B=8 S=2048, bf16
   gemm  the layer's gate/up projection as one SwiGLU GEMM: M=16384 N=2x11008 K=4096
   h2o   H2O score on the headline attention shape (B=4 H=32 S=4096 D=128, causal)
+  bwd   attention backward (preprocess + dK/dV + dQ kernels) on the headline shape, causal; TFLOP/s in
+        the usual convention of five matrix products (2.5 x the forward count); the seven products
+        the two kernels really issue (each recomputes S and dP) are reported as executed_tflops
   softmax  row softmax of a 32768 x 4096 bf16 score matrix (HBM-bound, GB/s of algorithmic bytes)
   rowstat  RMSNorm row statistic fused with the residual add on the layer's activations
         (16384 x 4096 bf16): HBM-bound, reported in GB/s of algorithmic bytes
@@ -39,7 +42,7 @@ def _time(fn, steps: int, warmup: int) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", choices=["c3", "c4", "c5", "gemm", "h2o", "rowstat", "softmax"], required=True)
+    ap.add_argument("--config", choices=["c3", "c4", "c5", "gemm", "h2o", "bwd", "rowstat", "softmax"], required=True)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -83,6 +86,20 @@ def main() -> None:
         ms = _time(lambda: ops.h2o_score(q, k, lse, causal=True), args.steps, args.warmup)
         flops = 1.0 * B * H * S * S * D  # one causal Q K^T product
         line.update(workload="h2o_score_bf16_causal_B4_H32_S4096_D128", dtype="bf16")
+    elif args.config == "bwd":
+        B, H, S, D = 4, 32, 4096, 128
+        q, k, v, g = (rnd(B, H, S, D).bfloat16() for _ in range(4))
+        out, lse = ops.fa_fwd(q, k, v, causal=True, return_lse=True)
+        ms = _time(lambda: ops.fa_bwd(q, k, v, out, g, lse, causal=True), args.steps, args.warmup)
+        delta = ops.fa_bwd_preprocess(out, g)
+        parts = {
+            "preprocess_ms": _time(lambda: ops.fa_bwd_preprocess(out, g), args.steps, args.warmup),
+            "dkdv_ms": _time(lambda: ops.fa_bwd_dkdv(q, k, v, g, lse, delta, causal=True), args.steps, args.warmup),
+            "dq_ms": _time(lambda: ops.fa_bwd_dq(q, k, v, g, lse, delta, causal=True), args.steps, args.warmup),
+        }
+        flops = 5.0 * B * H * S * S * D  # five causal products of 2 S^2 D / 2 flops each
+        line.update(workload="fa_bwd_bf16_causal_B4_H32_S4096_D128", dtype="bf16", **parts,
+                    executed_tflops=7.0 * B * H * S * S * D / ms / 1e9)
     elif args.config == "softmax":
         R, Cn = 32768, 4096
         xs = [rnd(R, Cn).bfloat16() for _ in range(3)]  # 3 x 268 MB in rotation: no launch finds its input in L2

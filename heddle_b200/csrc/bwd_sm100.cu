@@ -11,22 +11,58 @@
 // there.  The dK/dV kernel issues the products transposed (S^T = K Q^T, dP^T = V dO^T), so that a
 // key is a TMEM lane: P^T and dS^T are then exactly the A operands (from TMEM) of dV += P^T dO
 // and dK += dS^T Q, and each thread owns one key row.  The dQ kernel keeps queries on the lanes.
-// One CTA (192 threads): warps 0-3 turn scores into P / dS (one row per thread), warp 4 is the TMA
-// producer, warp 5 issues the MMAs.  The schedule is a plain one (S and dP single-buffered): this is
-// a first, correct version of a "next" row, not a tuned one.  head_dim 128, bf16 / fp16.
+// One CTA (320 threads): warps 0-7 turn scores into P / dS (a row is shared by two threads, warp w
+// takes columns [0,64) and warp w+4 columns [64,128) of the same 32 TMEM lanes; P stays in fp32
+// registers between the two phases), warp 8 is the TMA producer, warp 9 issues the MMAs.
+//
+// Schedules (n = step, one 128 x 128 tile of scores; A = scores -> P, B = dP -> dS):
+//   dK/dV  tensor pipe:  S(0) dP(0) | dV(n) S(n+1) | dK(n) dP(n+1) | ...
+//          TMEM is full (S^T, dP^T, dV, dK = 512 columns), P^T overwrites S^T and dS^T overwrites
+//          dP^T in place, so S(n+1) follows dV(n) and dP(n+1) follows dK(n) on the in-order tensor
+//          pipe; phase B(n) and the MMAs dK(n), dP(n+1) hide behind the chain A(n) -> dV(n) -> S(n+1).
+//   dQ     tensor pipe:  S(0) dP(0) S(1) | dP(n+1) dQ(n) S(n+2) | ...
+//          S is double-buffered (S0, S1, dP, dQ = 512 columns) and dS(n) is written over S(n), so the
+//          dP region is free as soon as phase B(n) has read it and phase A(n+1) hides behind dP(n+1).
+// head_dim 128, bf16 / fp16.
 #include "host_common.h"
 #include "ptx_sm100.cuh"
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 
 namespace hb {
 
-constexpr int kBwdThreads = 192;
-constexpr int kBwdStages = 2;
+constexpr int kBwdThreads = 320;
 constexpr int kBwdD = 128;
 constexpr uint32_t kBwdTileBytes = 128 * kBwdD * 2;  // one 128-row tile of a 16-bit tensor
 enum BwdRole : uint32_t { kBwdTma = 0x41, kBwdMma = 0x42, kBwdCons = 0x43, kBwdDrain = 0x44 };
+// Share of the exponentials evaluated on the FMA pipe instead of the MUFU: 0 none, 1 a quarter, 2 half.
+#ifndef HB_BWD_POLY
+#define HB_BWD_POLY 0
+#endif
+
+// Measurement builds (-DHB_BWD_PROF): every warp of the dQ kernel sums the cycles it spends in up to
+// eight sections of its loop; hb_debug_bwd_prof copies the sums out.
+#ifdef HB_BWD_PROF
+__device__ unsigned long long g_bwd_prof[148 * 10 * 8];
+#define BWD_PROF_DECL                                     \
+  unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; \
+  long long prof_t = clock64();
+#define BWD_PROF(i)                                              \
+  {                                                              \
+    const long long t_ = clock64();                              \
+    prof_acc[i] += static_cast<unsigned long long>(t_ - prof_t); \
+    prof_t = t_;                                                 \
+  }
+#define BWD_PROF_FLUSH                                                                                    \
+  if (lane == 0 && blockIdx.x < 148)                                                                      \
+    for (int i_ = 0; i_ < 8; ++i_) g_bwd_prof[(blockIdx.x * 10 + warp) * 8 + i_] = prof_acc[i_];
+#else
+#define BWD_PROF_DECL
+#define BWD_PROF(i)
+#define BWD_PROF_FLUSH
+#endif
 
 struct alignas(64) BwdParams {
   CUtensorMap tm_q, tm_k, tm_v, tm_do;
@@ -43,28 +79,42 @@ struct alignas(64) BwdParams {
   float scale_log2, scale;
 };
 
+// rings: A feeds the score product and the last product of the step, B the dP product (and dV)
+template <int kStagesA, int kStagesB, bool kStage>
 struct BwdSmem {
-  alignas(1024) uint8_t fixed[2][kBwdTileBytes];              // dkdv: K, V of the item;  dq: Q, dO of the item
-  alignas(1024) uint8_t ring[kBwdStages][2][kBwdTileBytes];   // dkdv: {Q, dO} per step;  dq: {K, V} per step
+  static constexpr int kSA = kStagesA, kSB = kStagesB;
+  alignas(1024) uint8_t fixed[2][kBwdTileBytes];        // dkdv: K, V of the item;  dq: Q, dO of the item
+  alignas(1024) uint8_t ring_a[kStagesA][kBwdTileBytes];  // dkdv: Q tiles;  dq: K tiles
+  alignas(1024) uint8_t ring_b[kStagesB][kBwdTileBytes];  // dkdv: dO tiles; dq: V tiles
   uint64_t fixed_full, fixed_empty;
-  uint64_t ring_full[kBwdStages], ring_empty[kBwdStages];
-  uint64_t s_full;     // MMA -> consumers: scores and dP of the step are in TMEM
-  uint64_t p_ready;    // consumers -> MMA: P / dS written back to TMEM
+  uint64_t a_full[kStagesA], a_empty[kStagesA];
+  uint64_t b_full[kStagesB], b_empty[kStagesB];
+  uint64_t s_full[2];  // MMA -> consumers: scores are in TMEM (dkdv uses [0] only)
+  uint64_t dp_full;    // MMA -> consumers: dP is in TMEM
+  uint64_t p_ready;    // consumers -> MMA: P written (dkdv only)
+  uint64_t ds_ready;   // consumers -> MMA: dS written, dP read
+  // warps 0-3 -> warps 4-7: columns [32,64) of a tile have been read (the upper warps' 16-bit results
+  // land there).  One completion per step and barrier (dkdv: [0] scores, [1] dP; dq: [score buffer]),
+  // so the lower warps can never be two phases ahead of a waiting upper warp.
+  uint64_t half_read[2];
   uint64_t acc_full;   // MMA -> consumers: the item's accumulators are complete
   uint64_t acc_empty;  // consumers -> MMA: accumulators read out
   uint64_t drain;
   uint32_t tmem_base, abort_flag;
-  alignas(16) float stage[4][2][2][128];  // dkdv: per consumer warp, double-buffered {-LSE*log2e, delta} of a query tile
+  // dkdv: per consumer warp, double-buffered {-LSE*log2e, delta} of a query tile
+  alignas(16) float stage[kStage ? 8 : 1][2][2][kStage ? 64 : 4];
 };
+using BwdSmemKv = BwdSmem<2, 2, true>;
+using BwdSmemQ = BwdSmem<3, 2, false>;
 
 // Shared-memory descriptor pieces (same conventions as the forward kernel)
 constexpr uint32_t kBwdDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
-constexpr uint32_t kBwdLboK = (16u >> 4) << 16;                // K-major operand
-constexpr uint32_t kBwdSub16 = (128u * 128u) >> 4;             // one 128-byte-wide, 128-row sub-tile in 16-byte units
-constexpr uint32_t kBwdLboMn = kBwdSub16 << 16;                // MN-major operand: next 64 head_dim columns
+constexpr uint32_t kBwdLboK = (16u >> 4) << 16;     // K-major operand
+constexpr uint32_t kBwdSub16 = (128u * 128u) >> 4;  // one 128-byte-wide, 128-row sub-tile in 16-byte units
+constexpr uint32_t kBwdLboMn = kBwdSub16 << 16;     // MN-major operand: next 64 head_dim columns
 __device__ __forceinline__ uint64_t bwd_desc(uint32_t lo) { return (static_cast<uint64_t>(kBwdDescHi) << 32) | lo; }
 
-// D[128 x 128] (+)= A[128 x 128(K = head_dim)] . B[128 x 128(K = head_dim)]^T, both operands K-major tiles in smem
+// D[128 x 128] = A[128 x head_dim] . B[128 x head_dim]^T, both operands K-major tiles in smem
 template <typename T>
 __device__ __forceinline__ void bwd_mma_kk(uint32_t d_tmem, const void* a_tile, const void* b_tile) {
   constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, 128, 128, 0, 0);
@@ -88,6 +138,7 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, con
 }
 
 __device__ __forceinline__ void bwd_load_tile(void* dst, const CUtensorMap* tm, uint64_t* bar, int row0, int h, int b) {
+  mbar_arrive_expect_tx(bar, kBwdTileBytes);
 #pragma unroll
   for (int hh = 0; hh < kBwdD / 64; ++hh)
     tma_load_4d(static_cast<uint8_t*>(dst) + hh * (128 * 128), tm, bar, hh * 64, row0, h, b);
@@ -106,18 +157,55 @@ __device__ __forceinline__ void bwd_store_row(T* dst, const uint32_t (&r)[32], f
   }
 }
 
-__device__ __forceinline__ void bwd_init(BwdSmem& s, const AbortCtx& ctx, const void* smem_raw) {
+// Four probabilities 2^(s * scale_log2 + nl) of one thread's row; with HB_BWD_POLY part of them on the FMA pipe.
+__device__ __forceinline__ void bwd_exp4(const uint32_t* sv, int e, uint64_t sc2, float4 l4, float* out) {
+#ifdef HB_BWD_KO_EXP  // measurement builds only: no exponentials (wrong results)
+  out[0] = __uint_as_float(sv[0]) + l4.x;
+  out[1] = __uint_as_float(sv[1]) + l4.y;
+  out[2] = __uint_as_float(sv[2]) + l4.z;
+  out[3] = __uint_as_float(sv[3]) + l4.w;
+  return;
+#endif
+  const uint64_t x0 = fma_f32x2(pack_f32x2(__uint_as_float(sv[0]), __uint_as_float(sv[1])), sc2, pack_f32x2(l4.x, l4.y));
+  const uint64_t x1 = fma_f32x2(pack_f32x2(__uint_as_float(sv[2]), __uint_as_float(sv[3])), sc2, pack_f32x2(l4.z, l4.w));
+  float a0, a1, b0, b1;
+  unpack_f32x2(x0, a0, a1);
+  out[0] = fast_exp2(a0);
+  out[1] = fast_exp2(a1);
+  const bool poly = (HB_BWD_POLY == 2) || (HB_BWD_POLY == 1 && (e & 4) != 0);
+  if (poly) {
+    exp2_poly_f32x2(x1, b0, b1);
+  } else {
+    unpack_f32x2(x1, b0, b1);
+    b0 = fast_exp2(b0);
+    b1 = fast_exp2(b1);
+  }
+  out[2] = b0;
+  out[3] = b1;
+}
+
+template <typename Smem>
+__device__ __forceinline__ void bwd_init(Smem& s, const AbortCtx& ctx, const void* smem_raw) {
   s.abort_flag = 0;
   mbar_init(&s.fixed_full, 1);
   mbar_init(&s.fixed_empty, 1);
-  for (int i = 0; i < kBwdStages; ++i) {
-    mbar_init(&s.ring_full[i], 1);
-    mbar_init(&s.ring_empty[i], 1);
+  for (int i = 0; i < Smem::kSA; ++i) {
+    mbar_init(&s.a_full[i], 1);
+    mbar_init(&s.a_empty[i], 1);
   }
-  mbar_init(&s.s_full, 1);
-  mbar_init(&s.p_ready, 4);
+  for (int i = 0; i < Smem::kSB; ++i) {
+    mbar_init(&s.b_full[i], 1);
+    mbar_init(&s.b_empty[i], 1);
+  }
+  mbar_init(&s.s_full[0], 1);
+  mbar_init(&s.s_full[1], 1);
+  mbar_init(&s.dp_full, 1);
+  mbar_init(&s.p_ready, 8);
+  mbar_init(&s.ds_ready, 8);
+  mbar_init(&s.half_read[0], 4);
+  mbar_init(&s.half_read[1], 4);
   mbar_init(&s.acc_full, 1);
-  mbar_init(&s.acc_empty, 4);
+  mbar_init(&s.acc_empty, 8);
   mbar_init(&s.drain, 1);
   fence_mbar_init();
   if ((smem_u32(smem_raw) & 1023u) != 0u) raise_abort(ctx, kStatusSmemMisaligned);
@@ -130,7 +218,8 @@ __device__ __forceinline__ void bwd_init(BwdSmem& s, const AbortCtx& ctx, const 
 template <typename T>
 __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  BwdSmem& s = *reinterpret_cast<BwdSmem*>(smem_raw);
+  using Smem = BwdSmemKv;
+  Smem& s = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{&s.abort_flag, p.status};
   if (threadIdx.x == 0) {
@@ -140,7 +229,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
     prefetch_tensormap(&p.tm_v);
     prefetch_tensormap(&p.tm_do);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
@@ -161,10 +250,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
     qt0 = p.causal ? max(0, (k0 - past) / 128) : 0;
   };
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (run && lane == 0) {
       // ---------------- TMA producer ----------------
-      uint32_t st = 0, phase = 1, f_phase = 1;
+      uint32_t cnt = 0, f_phase = 1;  // cnt: steps loaded so far (stage = cnt & 1 in both rings)
       bool ok = true;
       for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x) {
         int b, hkv, k0, qt0;
@@ -172,77 +261,116 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
         if (!mbar_wait(&s.fixed_empty, f_phase, ctx, kBwdTma)) break;
         f_phase ^= 1;
         mbar_arrive_expect_tx(&s.fixed_full, 2 * kBwdTileBytes);
-        bwd_load_tile(s.fixed[0], &p.tm_k, &s.fixed_full, k0, hkv, b);
-        bwd_load_tile(s.fixed[1], &p.tm_v, &s.fixed_full, k0, hkv, b);
+#pragma unroll
+        for (int hh = 0; hh < kBwdD / 64; ++hh) {
+          tma_load_4d(s.fixed[0] + hh * (128 * 128), &p.tm_k, &s.fixed_full, hh * 64, k0, hkv, b);
+          tma_load_4d(s.fixed[1] + hh * (128 * 128), &p.tm_v, &s.fixed_full, hh * 64, k0, hkv, b);
+        }
         for (int hg = 0; ok && hg < p.group; ++hg) {
           const int hq = hkv * p.group + hg;
-          for (int qt = qt0; qt < p.nqb; ++qt) {
-            if (!mbar_wait(&s.ring_empty[st], phase, ctx, kBwdTma)) {
+          for (int qt = qt0; qt < p.nqb; ++qt, ++cnt) {
+            const uint32_t st = cnt & 1u, ph = ((cnt >> 1) & 1u) ^ 1u;
+            if (!mbar_wait(&s.a_empty[st], ph, ctx, kBwdTma)) {
               ok = false;
               break;
             }
-            mbar_arrive_expect_tx(&s.ring_full[st], 2 * kBwdTileBytes);
-            bwd_load_tile(s.ring[st][0], &p.tm_q, &s.ring_full[st], qt * 128, hq, b);
-            bwd_load_tile(s.ring[st][1], &p.tm_do, &s.ring_full[st], qt * 128, hq, b);
-            if (++st == kBwdStages) {
-              st = 0;
-              phase ^= 1;
+            bwd_load_tile(s.ring_a[st], &p.tm_q, &s.a_full[st], qt * 128, hq, b);
+            if (!mbar_wait(&s.b_empty[st], ph, ctx, kBwdTma)) {
+              ok = false;
+              break;
             }
+            bwd_load_tile(s.ring_b[st], &p.tm_do, &s.b_full[st], qt * 128, hq, b);
           }
         }
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (run) {
       // ---------------- MMA issuer (warp-uniform, elected lane issues) ----------------
       const bool leader = elect_one();
-      uint32_t st = 0, phase = 0, f_phase = 0, s_cnt = 0, items = 0;
+      uint32_t cnt = 0, f_phase = 0, items = 0;  // cnt: global step counter
       bool ok = true;
+      BWD_PROF_DECL
+      auto full_a = [&](uint32_t c) { return mbar_wait_warp(&s.a_full[c & 1u], (c >> 1) & 1u, ctx, kBwdMma); };
+      auto full_b = [&](uint32_t c) { return mbar_wait_warp(&s.b_full[c & 1u], (c >> 1) & 1u, ctx, kBwdMma); };
       for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x, ++items) {
         int b, hkv, k0, qt0;
         item_of(g, b, hkv, k0, qt0);
+        const int n_steps = p.group * (p.nqb - qt0);
         if (!mbar_wait_warp(&s.fixed_full, f_phase, ctx, kBwdMma)) break;
         f_phase ^= 1;
-        bool first = true;
-        for (int hg = 0; ok && hg < p.group; ++hg) {
-          for (int qt = qt0; qt < p.nqb; ++qt) {
-            if (!mbar_wait_warp(&s.ring_full[st], phase, ctx, kBwdMma)) {
+        // prologue: S(0), dP(0)
+        if (!full_a(cnt)) break;
+        tc_fence_after();
+        if (leader) {
+          bwd_mma_kk<T>(tmem + 0, s.fixed[0], s.ring_a[cnt & 1u]);  // S^T = K Q^T
+          umma_commit(&s.s_full[0]);
+        }
+        __syncwarp();
+        if (!full_b(cnt)) break;
+        tc_fence_after();
+        if (leader) {
+          bwd_mma_kk<T>(tmem + 128, s.fixed[1], s.ring_b[cnt & 1u]);  // dP^T = V dO^T
+          umma_commit(&s.dp_full);
+        }
+        __syncwarp();
+        BWD_PROF(0)
+        for (int n = 0; n < n_steps; ++n, ++cnt) {
+          const uint32_t st = cnt & 1u, nx = (cnt + 1) & 1u, par = cnt & 1u;
+          const bool more = n + 1 < n_steps;
+          // the first accumulation of the item overwrites dV, dK: the previous item's read-out must be over
+          if (n == 0 && !mbar_wait_warp(&s.acc_empty, (items & 1u) ^ 1u, ctx, kBwdMma)) {
+            ok = false;
+            break;
+          }
+          if (!mbar_wait_warp(&s.p_ready, par, ctx, kBwdMma)) {
+            ok = false;
+            break;
+          }
+          BWD_PROF(1)
+          tc_fence_after();
+          if (leader) {
+            bwd_mma_ts<T>(tmem + 256, tmem + 0, s.ring_b[st], n > 0 ? 1u : 0u);  // dV += P^T dO
+            umma_commit(&s.b_empty[st]);
+          }
+          __syncwarp();
+          BWD_PROF(2)
+          if (more) {
+            // the Q tile of the next step was requested when dK of the previous step completed
+            if (!full_a(cnt + 1)) {
               ok = false;
               break;
             }
+            BWD_PROF(3)
             tc_fence_after();
             if (leader) {
-              bwd_mma_kk<T>(tmem + 0, s.fixed[0], s.ring[st][0]);    // S^T  = K Q^T
-              bwd_mma_kk<T>(tmem + 128, s.fixed[1], s.ring[st][1]);  // dP^T = V dO^T
-              umma_commit(&s.s_full);
+              bwd_mma_kk<T>(tmem + 0, s.fixed[0], s.ring_a[nx]);  // S^T of the next step, over P^T
+              umma_commit(&s.s_full[0]);
             }
             __syncwarp();
-            if (!mbar_wait_warp(&s.p_ready, s_cnt & 1, ctx, kBwdMma)) {
+            BWD_PROF(4)
+            if (!full_b(cnt + 1)) {
               ok = false;
               break;
-            }
-            ++s_cnt;
-            if (first) {
-              // the first accumulation of the item overwrites dV, dK: the previous item's read-out must be over
-              if (!mbar_wait_warp(&s.acc_empty, (items & 1) ^ 1, ctx, kBwdMma)) {
-                ok = false;
-                break;
-              }
-            }
-            tc_fence_after();
-            if (leader) {
-              bwd_mma_ts<T>(tmem + 256, tmem + 0, s.ring[st][1], first ? 0u : 1u);    // dV += P^T dO
-              bwd_mma_ts<T>(tmem + 384, tmem + 128, s.ring[st][0], first ? 0u : 1u);  // dK += dS^T Q
-              umma_commit(&s.ring_empty[st]);
-            }
-            __syncwarp();
-            first = false;
-            if (++st == kBwdStages) {
-              st = 0;
-              phase ^= 1;
             }
           }
+          if (!mbar_wait_warp(&s.ds_ready, par, ctx, kBwdMma)) {
+            ok = false;
+            break;
+          }
+          BWD_PROF(5)
+          tc_fence_after();
+          if (leader) {
+            bwd_mma_ts<T>(tmem + 384, tmem + 128, s.ring_a[st], n > 0 ? 1u : 0u);  // dK += dS^T Q
+            umma_commit(&s.a_empty[st]);
+            if (more) {
+              bwd_mma_kk<T>(tmem + 128, s.fixed[1], s.ring_b[nx]);  // dP^T of the next step, over dS^T
+              umma_commit(&s.dp_full);
+            }
+          }
+          __syncwarp();
+          BWD_PROF(6)
         }
         if (ok && leader) {
           umma_commit(&s.acc_full);
@@ -251,6 +379,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
         __syncwarp();
       }
       __syncwarp();
+      BWD_PROF_FLUSH
       if (s.abort_flag && lane == 0) {
         umma_commit(&s.drain);
         mbar_wait(&s.drain, 0, ctx, kBwdDrain);
@@ -258,10 +387,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
     }
     __syncwarp();
   } else if (run) {
-    // ---------------- consumers: one key per thread ----------------
-    const int key_in_tile = warp * 32 + lane;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    uint32_t s_cnt = 0, items = 0, buf = 0;
+    // ---------------- consumers: one key per pair of threads ----------------
+    const int slab = warp & 3, half = warp >> 2;
+    const int key_in_tile = slab * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(slab * 32) << 16;
+    const uint32_t col_in = static_cast<uint32_t>(half * 64);   // fp32 columns this thread reads
+    const uint32_t col_out = static_cast<uint32_t>(half * 32);  // 16-bit columns it writes
+    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+    uint32_t cnt = 0, items = 0;
     bool ok = true;
     for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x, ++items) {
       int b, hkv, k0, qt0;
@@ -271,72 +404,125 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
         const int hq = hkv * p.group + hg;
         const float* lse_row = p.lse + (static_cast<long long>(b) * p.Hq + hq) * p.Sq;
         const float* dl_row = p.delta + (static_cast<long long>(b) * p.Hq + hq) * p.Sq;
-        for (int qt = qt0; qt < p.nqb; ++qt) {
-          // this warp's copy of the tile's per-query terms; queries past Sq get -inf, so P is exactly 0
-          float* nl = s.stage[warp][buf][0];
-          float* dl = s.stage[warp][buf][1];
-          buf ^= 1;
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int q = qt * 128 + lane * 4 + u;
-            nl[lane * 4 + u] = (q < p.Sq) ? -__ldg(lse_row + q) * 1.4426950408889634f : -INFINITY;
-            dl[lane * 4 + u] = (q < p.Sq) ? __ldg(dl_row + q) : 0.f;
+        for (int qt = qt0; qt < p.nqb; ++qt, ++cnt) {
+          // this warp's copy of the per-query terms of its 64 queries; queries past Sq get -inf (P = 0)
+          float2* nl2 = reinterpret_cast<float2*>(s.stage[warp][cnt & 1u][0]);
+          float2* dl2 = reinterpret_cast<float2*>(s.stage[warp][cnt & 1u][1]);
+          {
+            const int q = qt * 128 + half * 64 + lane * 2;
+            float2 nv, dv;
+            nv.x = (q < p.Sq) ? -__ldg(lse_row + q) * 1.4426950408889634f : -INFINITY;
+            nv.y = (q + 1 < p.Sq) ? -__ldg(lse_row + q + 1) * 1.4426950408889634f : -INFINITY;
+            dv.x = (q < p.Sq) ? __ldg(dl_row + q) : 0.f;
+            dv.y = (q + 1 < p.Sq) ? __ldg(dl_row + q + 1) : 0.f;
+            nl2[lane] = nv;
+            dl2[lane] = dv;
           }
           __syncwarp();
-          if (!mbar_wait_warp(&s.s_full, s_cnt & 1, ctx, kBwdCons)) {
+          const float4* nl4 = reinterpret_cast<const float4*>(nl2);
+          const float4* dl4 = reinterpret_cast<const float4*>(dl2);
+          // ---- phase A: scores -> P (kept in registers, 16-bit copy over S^T for dV += P^T dO) ----
+          if (!mbar_wait_warp(&s.s_full[0], cnt & 1u, ctx, kBwdCons)) {
             ok = false;
             break;
           }
-          ++s_cnt;
           tc_fence_after();
-          // causal: key visible to query q iff key <= q + past
-          const int q_min = p.causal ? (key - past - qt * 128) : -1;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t sv[32], dv[32], pk[16], dk[16];
-            tmem_ld32(tmem + lane_off + c * 32, sv);
-            tmem_ld32(tmem + lane_off + 128 + c * 32, dv);
+          float pr[64];
+          {
+            uint32_t sv[64], pk[32];
+            tmem_ld32(tmem + lane_off + col_in, sv);
+            tmem_ld32(tmem + lane_off + col_in + 32, sv + 32);
             tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              float pe[2], de[2];
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                const int qi = c * 32 + e + u;
-                float pr = fast_exp2(fmaf(__uint_as_float(sv[e + u]), p.scale_log2, nl[qi]));
-                pr = (qi >= q_min) ? pr : 0.f;
-                pe[u] = pr;
-                de[u] = pr * (__uint_as_float(dv[e + u]) - dl[qi]);
-              }
-              pk[e / 2] = Pack2<T>::pack(pe[0], pe[1]);
-              dk[e / 2] = Pack2<T>::pack(de[0], de[1]);
+            if (half == 0) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&s.half_read[0]);
             }
-            // P^T chunk c lands on columns of S^T chunks <= c, which are already in registers
-            tmem_st16(tmem + lane_off + c * 16, pk);
-            tmem_st16(tmem + lane_off + 128 + c * 16, dk);
+            // causal: key visible to query q iff key <= q + past; only tiles on the diagonal need the test
+            const bool need_mask = p.causal && (qt * 128 < k0 + 127 - past);
+            const int q_min = key - past - qt * 128 - half * 64;  // first visible query, relative to this thread's columns
+#pragma unroll
+            for (int e = 0; e < 64; e += 4) {
+              bwd_exp4(&sv[e], e, sc2, nl4[e >> 2], &pr[e]);
+              if (need_mask) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) pr[e + u] = (e + u >= q_min) ? pr[e + u] : 0.f;
+              }
+              pk[e / 2] = Pack2<T>::pack(pr[e], pr[e + 1]);
+              pk[e / 2 + 1] = Pack2<T>::pack(pr[e + 2], pr[e + 3]);
+            }
+            // the lower warps overwrite columns they have read themselves; the upper warps' P^T lands on
+            // columns [32,64), which the lower warps have read once half_read completes
+            if (half == 1) {
+              if (!mbar_wait_warp(&s.half_read[0], cnt & 1u, ctx, kBwdCons)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+            tmem_st32(tmem + lane_off + col_out, pk);
           }
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&s.p_ready);
+          // ---- phase B: dP -> dS = P o (dP - delta), 16-bit over dP^T for dK += dS^T Q ----
+          if (!mbar_wait_warp(&s.dp_full, cnt & 1u, ctx, kBwdCons)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          {
+            uint32_t dv[64], dk[32];
+            tmem_ld32(tmem + lane_off + 128 + col_in, dv);
+            tmem_ld32(tmem + lane_off + 128 + col_in + 32, dv + 32);
+            tmem_wait_ld();
+            if (half == 0) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&s.half_read[1]);
+            }
+#pragma unroll
+            for (int e = 0; e < 64; e += 4) {
+              const float4 d4 = dl4[e >> 2];
+              const float x0 = pr[e] * (__uint_as_float(dv[e]) - d4.x);
+              const float x1 = pr[e + 1] * (__uint_as_float(dv[e + 1]) - d4.y);
+              const float x2 = pr[e + 2] * (__uint_as_float(dv[e + 2]) - d4.z);
+              const float x3 = pr[e + 3] * (__uint_as_float(dv[e + 3]) - d4.w);
+              dk[e / 2] = Pack2<T>::pack(x0, x1);
+              dk[e / 2 + 1] = Pack2<T>::pack(x2, x3);
+            }
+            if (half == 1) {
+              if (!mbar_wait_warp(&s.half_read[1], cnt & 1u, ctx, kBwdCons)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+            tmem_st32(tmem + lane_off + 128 + col_out, dk);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.ds_ready);
         }
       }
       if (!ok) break;
-      // read-out: dV as is, dK times the softmax scale
-      if (!mbar_wait_warp(&s.acc_full, items & 1, ctx, kBwdCons)) break;
+      // read-out: dV as is, dK times the softmax scale; each thread stores its 64 columns of the row
+      if (!mbar_wait_warp(&s.acc_full, items & 1u, ctx, kBwdCons)) break;
       tc_fence_after();
       const bool live = key < p.Skv;
-      T* dv_row = static_cast<T*>(p.dv) + ((static_cast<long long>(b) * p.Hkv + hkv) * p.Skv + key) * kBwdD;
-      T* dk_row = static_cast<T*>(p.dk) + ((static_cast<long long>(b) * p.Hkv + hkv) * p.Skv + key) * kBwdD;
+      T* dv_row = static_cast<T*>(p.dv) + ((static_cast<long long>(b) * p.Hkv + hkv) * p.Skv + key) * kBwdD + col_in;
+      T* dk_row = static_cast<T*>(p.dk) + ((static_cast<long long>(b) * p.Hkv + hkv) * p.Skv + key) * kBwdD + col_in;
 #pragma unroll 1
-      for (int c = 0; c < kBwdD / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         __syncwarp();
-        tmem_ld32(tmem + lane_off + 256 + c * 32, r);
+        tmem_ld32(tmem + lane_off + 256 + col_in + c * 32, r);
         tmem_wait_ld();
         if (live) bwd_store_row<T>(dv_row + c * 32, r, 1.0f);
         __syncwarp();
-        tmem_ld32(tmem + lane_off + 384 + c * 32, r);
+        tmem_ld32(tmem + lane_off + 384 + col_in + c * 32, r);
         tmem_wait_ld();
         if (live) bwd_store_row<T>(dk_row + c * 32, r, p.scale);
       }
@@ -348,7 +534,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -356,12 +542,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
 
 // ------------------------------------------------------------------------------------------
 // dQ: one CTA per (batch, query head, 128-query tile); loops over the key tiles the queries see.
-// TMEM: S [0,128) dP [128,256) dQ [256,384).
+// TMEM: S buffers [0,128) [128,256), dP [256,384), dQ [384,512).
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  BwdSmem& s = *reinterpret_cast<BwdSmem*>(smem_raw);
+  using Smem = BwdSmemQ;
+  Smem& s = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{&s.abort_flag, p.status};
   if (threadIdx.x == 0) {
@@ -371,7 +558,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
     prefetch_tensormap(&p.tm_v);
     prefetch_tensormap(&p.tm_do);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
@@ -392,9 +579,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
     nk = p.causal ? min(p.nkb, (min(q0 + 127, p.Sq - 1) + past) / 128 + 1) : p.nkb;
   };
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (run && lane == 0) {
-      uint32_t st = 0, phase = 1, f_phase = 1;
+      // ---------------- TMA producer ----------------
+      uint32_t cnt = 0, f_phase = 1;
       bool ok = true;
       for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x) {
         int b, hq, q0, nk;
@@ -403,67 +591,101 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
         if (!mbar_wait(&s.fixed_empty, f_phase, ctx, kBwdTma)) break;
         f_phase ^= 1;
         mbar_arrive_expect_tx(&s.fixed_full, 2 * kBwdTileBytes);
-        bwd_load_tile(s.fixed[0], &p.tm_q, &s.fixed_full, q0, hq, b);
-        bwd_load_tile(s.fixed[1], &p.tm_do, &s.fixed_full, q0, hq, b);
-        for (int kt = 0; kt < nk; ++kt) {
-          if (!mbar_wait(&s.ring_empty[st], phase, ctx, kBwdTma)) {
+#pragma unroll
+        for (int hh = 0; hh < kBwdD / 64; ++hh) {
+          tma_load_4d(s.fixed[0] + hh * (128 * 128), &p.tm_q, &s.fixed_full, hh * 64, q0, hq, b);
+          tma_load_4d(s.fixed[1] + hh * (128 * 128), &p.tm_do, &s.fixed_full, hh * 64, q0, hq, b);
+        }
+        for (int kt = 0; kt < nk; ++kt, ++cnt) {
+          const uint32_t sa = cnt % 3u, pa = ((cnt / 3u) & 1u) ^ 1u;
+          const uint32_t sb = cnt & 1u, pb = ((cnt >> 1) & 1u) ^ 1u;
+          if (!mbar_wait(&s.a_empty[sa], pa, ctx, kBwdTma)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&s.ring_full[st], 2 * kBwdTileBytes);
-          bwd_load_tile(s.ring[st][0], &p.tm_k, &s.ring_full[st], kt * 128, hkv, b);
-          bwd_load_tile(s.ring[st][1], &p.tm_v, &s.ring_full[st], kt * 128, hkv, b);
-          if (++st == kBwdStages) {
-            st = 0;
-            phase ^= 1;
+          bwd_load_tile(s.ring_a[sa], &p.tm_k, &s.a_full[sa], kt * 128, hkv, b);
+          if (!mbar_wait(&s.b_empty[sb], pb, ctx, kBwdTma)) {
+            ok = false;
+            break;
           }
+          bwd_load_tile(s.ring_b[sb], &p.tm_v, &s.b_full[sb], kt * 128, hkv, b);
         }
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (run) {
+      // ---------------- MMA issuer ----------------
       const bool leader = elect_one();
-      uint32_t st = 0, phase = 0, f_phase = 0, s_cnt = 0, items = 0;
+      uint32_t cnt = 0, f_phase = 0, items = 0;  // cnt: global step counter
       bool ok = true;
+      BWD_PROF_DECL
+      // S(c) = Q K(c)^T into score buffer c & 1
+      auto issue_s = [&](uint32_t c) -> bool {
+        if (!mbar_wait_warp(&s.a_full[c % 3u], (c / 3u) & 1u, ctx, kBwdMma)) return false;
+        tc_fence_after();
+        if (leader) {
+          bwd_mma_kk<T>(tmem + (c & 1u) * 128u, s.fixed[0], s.ring_a[c % 3u]);
+          umma_commit(&s.s_full[c & 1u]);
+        }
+        __syncwarp();
+        return true;
+      };
+      // dP(c) = dO V(c)^T; V(c) is not needed again
+      auto issue_dp = [&](uint32_t c) -> bool {
+        if (!mbar_wait_warp(&s.b_full[c & 1u], (c >> 1) & 1u, ctx, kBwdMma)) return false;
+        tc_fence_after();
+        if (leader) {
+          bwd_mma_kk<T>(tmem + 256, s.fixed[1], s.ring_b[c & 1u]);
+          umma_commit(&s.dp_full);
+          umma_commit(&s.b_empty[c & 1u]);
+        }
+        __syncwarp();
+        return true;
+      };
       for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x, ++items) {
         int b, hq, q0, nk;
         item_of(g, b, hq, q0, nk);
         if (!mbar_wait_warp(&s.fixed_full, f_phase, ctx, kBwdMma)) break;
         f_phase ^= 1;
-        for (int kt = 0; kt < nk; ++kt) {
-          if (!mbar_wait_warp(&s.ring_full[st], phase, ctx, kBwdMma)) {
+        if (!issue_s(cnt) || !issue_dp(cnt)) break;
+        if (nk > 1 && !issue_s(cnt + 1)) break;
+        BWD_PROF(0)
+        for (int n = 0; n < nk; ++n, ++cnt) {
+          // the V tile of the next dP was requested a step ago: waited for before the consumers' result,
+          // so that dP and dQ go out back to back
+          if ((n + 1 < nk && !mbar_wait_warp(&s.b_full[(cnt + 1) & 1u], ((cnt + 1) >> 1) & 1u, ctx, kBwdMma)) ||
+              (n == 0 && !mbar_wait_warp(&s.acc_empty, (items & 1u) ^ 1u, ctx, kBwdMma))) {
             ok = false;
             break;
           }
+          BWD_PROF(1)
+          if (!mbar_wait_warp(&s.ds_ready, cnt & 1u, ctx, kBwdMma)) {
+            ok = false;
+            break;
+          }
+          BWD_PROF(2)
           tc_fence_after();
           if (leader) {
-            bwd_mma_kk<T>(tmem + 0, s.fixed[0], s.ring[st][0]);    // S  = Q K^T
-            bwd_mma_kk<T>(tmem + 128, s.fixed[1], s.ring[st][1]);  // dP = dO V^T
-            umma_commit(&s.s_full);
-          }
-          __syncwarp();
-          if (!mbar_wait_warp(&s.p_ready, s_cnt & 1, ctx, kBwdMma)) {
-            ok = false;
-            break;
-          }
-          ++s_cnt;
-          if (kt == 0) {
-            if (!mbar_wait_warp(&s.acc_empty, (items & 1) ^ 1, ctx, kBwdMma)) {
-              ok = false;
-              break;
+            // dP of the step has been read and dS written over S: the next dP goes first, phase B of the
+            // next step waits for it
+            if (n + 1 < nk) {
+              bwd_mma_kk<T>(tmem + 256, s.fixed[1], s.ring_b[(cnt + 1) & 1u]);
+              umma_commit(&s.dp_full);
+              umma_commit(&s.b_empty[(cnt + 1) & 1u]);
             }
-          }
-          tc_fence_after();
-          if (leader) {
-            bwd_mma_ts<T>(tmem + 256, tmem + 128, s.ring[st][0], kt > 0 ? 1u : 0u);  // dQ += dS K
-            umma_commit(&s.ring_empty[st]);
+            bwd_mma_ts<T>(tmem + 384, tmem + (cnt & 1u) * 128u, s.ring_a[cnt % 3u], n > 0 ? 1u : 0u);  // dQ += dS K
+            umma_commit(&s.a_empty[cnt % 3u]);
           }
           __syncwarp();
-          if (++st == kBwdStages) {
-            st = 0;
-            phase ^= 1;
+          BWD_PROF(3)
+          // the K tile two steps ahead was requested when dQ of the previous step completed; its scores
+          // are not needed before the next step's phase A
+          if (n + 2 < nk && !issue_s(cnt + 2)) {
+            ok = false;
+            break;
           }
+          BWD_PROF(4)
         }
         if (ok && leader) {
           umma_commit(&s.acc_full);
@@ -472,6 +694,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
         __syncwarp();
       }
       __syncwarp();
+      BWD_PROF_FLUSH
       if (s.abort_flag && lane == 0) {
         umma_commit(&s.drain);
         mbar_wait(&s.drain, 0, ctx, kBwdDrain);
@@ -479,11 +702,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
     }
     __syncwarp();
   } else if (run) {
-    // ---------------- consumers: one query per thread ----------------
-    const int row_in_tile = warp * 32 + lane;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    uint32_t s_cnt = 0, items = 0;
+    // ---------------- consumers: one query per pair of threads ----------------
+    const int slab = warp & 3, half = warp >> 2;
+    const int row_in_tile = slab * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(slab * 32) << 16;
+    const uint32_t col_in = static_cast<uint32_t>(half * 64);
+    const uint32_t col_out = static_cast<uint32_t>(half * 32);
+    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+    uint32_t cnt = 0, items = 0;
     bool ok = true;
+    BWD_PROF_DECL
     for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x, ++items) {
       int b, hq, q0, nk;
       item_of(g, b, hq, q0, nk);
@@ -492,90 +720,146 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
       const long long stat = (static_cast<long long>(b) * p.Hq + hq) * p.Sq + q;
       const float nlse2 = live ? -__ldg(p.lse + stat) * 1.4426950408889634f : -INFINITY;
       const float dlt = live ? __ldg(p.delta + stat) : 0.f;
-      for (int kt = 0; kt < nk; ++kt) {
-        if (!mbar_wait_warp(&s.s_full, s_cnt & 1, ctx, kBwdCons)) {
+      const float4 l4 = make_float4(nlse2, nlse2, nlse2, nlse2);
+      for (int kt = 0; kt < nk; ++kt, ++cnt) {
+        const uint32_t sbuf = tmem + lane_off + (cnt & 1u) * 128u;
+        // ---- phase A: scores -> P in registers ----
+        if (!mbar_wait_warp(&s.s_full[cnt & 1u], (cnt >> 1) & 1u, ctx, kBwdCons)) {
           ok = false;
           break;
         }
-        ++s_cnt;
         tc_fence_after();
-        // keys this query sees in the tile: key <= q + past (causal) and key < Skv
-        int lim = p.Skv - 1 - kt * 128;
-        if (p.causal) lim = min(lim, q + past - kt * 128);
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t sv[32], dv[32], dk[16];
-          tmem_ld32(tmem + lane_off + c * 32, sv);
-          tmem_ld32(tmem + lane_off + 128 + c * 32, dv);
+        BWD_PROF(0)
+        float pr[64];
+        {
+          uint32_t sv[64];
+          tmem_ld32(sbuf + col_in, sv);
+          tmem_ld32(sbuf + col_in + 32, sv + 32);
           tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float de[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              float pr = fast_exp2(fmaf(__uint_as_float(sv[e + u]), p.scale_log2, nlse2));
-              pr = (c * 32 + e + u <= lim) ? pr : 0.f;
-              de[u] = pr * (__uint_as_float(dv[e + u]) - dlt);
-            }
-            dk[e / 2] = Pack2<T>::pack(de[0], de[1]);
+          BWD_PROF(1)
+          if (half == 0) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.half_read[cnt & 1u]);
           }
-          tmem_st16(tmem + lane_off + 128 + c * 16, dk);
+          // keys this query sees among this thread's columns: key <= q + past (causal) and key < Skv
+          int lim = p.Skv - 1 - kt * 128;
+          if (p.causal) lim = min(lim, q + past - kt * 128);
+          lim -= half * 64;
+          const bool need_mask = (kt * 128 + 127 >= p.Skv) || (p.causal && kt * 128 + 127 > q0 + past);
+#pragma unroll
+          for (int e = 0; e < 64; e += 4) {
+            bwd_exp4(&sv[e], e, sc2, l4, &pr[e]);
+            if (need_mask) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) pr[e + u] = (e + u <= lim) ? pr[e + u] : 0.f;
+            }
+          }
+        }
+        BWD_PROF(2)
+        // ---- phase B: dP -> dS, 16-bit over the score buffer of the step ----
+        if (!mbar_wait_warp(&s.dp_full, cnt & 1u, ctx, kBwdCons)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        BWD_PROF(3)
+        {
+          uint32_t dv[64], dk[32];
+          tmem_ld32(tmem + lane_off + 256 + col_in, dv);
+          tmem_ld32(tmem + lane_off + 256 + col_in + 32, dv + 32);
+          tmem_wait_ld();
+          BWD_PROF(4)
+#pragma unroll
+          for (int e = 0; e < 64; e += 2) {
+            const float x0 = pr[e] * (__uint_as_float(dv[e]) - dlt);
+            const float x1 = pr[e + 1] * (__uint_as_float(dv[e + 1]) - dlt);
+            dk[e / 2] = Pack2<T>::pack(x0, x1);
+          }
+          BWD_PROF(5)
+          // the upper warps' dS lands on score columns [32,64), which the lower warps read in phase A
+          if (half == 1) {
+            if (!mbar_wait_warp(&s.half_read[cnt & 1u], (cnt >> 1) & 1u, ctx, kBwdCons)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+          }
+          BWD_PROF(6)
+          tmem_st32(sbuf + col_out, dk);
         }
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s.p_ready);
+        if (lane == 0) mbar_arrive(&s.ds_ready);
+        BWD_PROF(7)
       }
       if (!ok) break;
-      if (!mbar_wait_warp(&s.acc_full, items & 1, ctx, kBwdCons)) break;
+      if (!mbar_wait_warp(&s.acc_full, items & 1u, ctx, kBwdCons)) break;
       tc_fence_after();
-      T* dq_row = static_cast<T*>(p.dq) + stat * kBwdD;
+      T* dq_row = static_cast<T*>(p.dq) + stat * kBwdD + col_in;
 #pragma unroll 1
-      for (int c = 0; c < kBwdD / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         __syncwarp();
-        tmem_ld32(tmem + lane_off + 256 + c * 32, r);
+        tmem_ld32(tmem + lane_off + 384 + col_in + c * 32, r);
         tmem_wait_ld();
         if (live) bwd_store_row<T>(dq_row + c * 32, r, p.scale);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.acc_empty);
+      BWD_PROF(0)
     }
+    BWD_PROF_FLUSH
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
 }
 
 // ------------------------------------------------------------------------------------------
-// delta = rowsum(O o dO): one warp per row, 8 bytes per lane (head_dim 128)
+// delta = rowsum(O o dO): HBM-bound (reads 2 x 256 B per row, writes 4 B).  Sixteen lanes share a row
+// (16 bytes each), a warp covers eight rows with all eight 16-byte loads of a lane in flight at once.
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) fa_bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
                                                                  float* __restrict__ delta, int B, int H, int S,
                                                                  long long o_sb, long long o_sh, long long o_ss,
                                                                  long long g_sb, long long g_sh, long long g_ss) {
-  const long long row = blockIdx.x * 8ll + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= static_cast<long long>(B) * H * S) return;
-  const int sq = static_cast<int>(row % S);
-  const long long bh = row / S;
-  const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
-  const uint2 a = *reinterpret_cast<const uint2*>(o + b * o_sb + h * o_sh + sq * o_ss + lane * 4);
-  const uint2 g = *reinterpret_cast<const uint2*>(d_o + b * g_sb + h * g_sh + sq * g_ss + lane * 4);
-  const T* ap = reinterpret_cast<const T*>(&a);
-  const T* gp = reinterpret_cast<const T*>(&g);
-  float acc = 0.f;
+  const int lane = threadIdx.x & 31, sub = lane >> 4, l16 = lane & 15;
+  const long long total = static_cast<long long>(B) * H * S;
+  const long long row0 = (blockIdx.x * 8ll + (threadIdx.x >> 5)) * 8;
+  uint4 a[4], g[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) acc += static_cast<float>(ap[e]) * static_cast<float>(gp[e]);
+  for (int i = 0; i < 4; ++i) {
+    const long long row = row0 + i * 2 + sub;
+    a[i] = make_uint4(0u, 0u, 0u, 0u);
+    g[i] = a[i];
+    if (row < total) {
+      const int sq = static_cast<int>(row % S);
+      const long long bh = row / S;
+      const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
+      a[i] = *reinterpret_cast<const uint4*>(o + b * o_sb + h * o_sh + sq * o_ss + l16 * 8);
+      g[i] = *reinterpret_cast<const uint4*>(d_o + b * g_sb + h * g_sh + sq * g_ss + l16 * 8);
+    }
+  }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) delta[row] = acc;
+  for (int i = 0; i < 4; ++i) {
+    const T* ap = reinterpret_cast<const T*>(&a[i]);
+    const T* gp = reinterpret_cast<const T*>(&g[i]);
+    float acc = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc = fmaf(static_cast<float>(ap[e]), static_cast<float>(gp[e]), acc);
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    const long long row = row0 + i * 2 + sub;
+    if (l16 == 0 && row < total) delta[row] = acc;
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -633,16 +917,16 @@ static int bwd_fill(const hb_fa_bwd_args* a, BwdParams& p, const DeviceState* st
   return HB_OK;
 }
 
-template <typename K>
+template <typename Smem, typename K>
 static int bwd_launch(K kernel, const BwdParams& p, int grid, const DeviceState* st, cudaStream_t stream, bool* configured) {
-  if ((int)sizeof(BwdSmem) > st->smem_optin)
+  if ((int)sizeof(Smem) > st->smem_optin)
     return set_error(HB_ERR_UNSUPPORTED, "attention backward needs %d bytes of shared memory per CTA, the device offers %d",
-                     (int)sizeof(BwdSmem), st->smem_optin);
+                     (int)sizeof(Smem), st->smem_optin);
   if (!configured[st->device & 63]) {
-    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(BwdSmem)));
+    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
     configured[st->device & 63] = true;
   }
-  kernel<<<grid, kBwdThreads, sizeof(BwdSmem), stream>>>(p);
+  kernel<<<grid, kBwdThreads, sizeof(Smem), stream>>>(p);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB_OK;
 }
@@ -657,14 +941,14 @@ extern "C" int hb_fa_bwd_preprocess(const hb_fa_bwd_args* a) {
   if (a->B == 0 || a->Sq == 0) return HB_OK;
   if (a->o == nullptr || a->d_o == nullptr || a->delta == nullptr)
     return set_error(HB_ERR_BAD_ARG, "hb_fa_bwd_preprocess: o, d_o and delta must be non-NULL");
-  if ((reinterpret_cast<uintptr_t>(a->o) & 7) || (reinterpret_cast<uintptr_t>(a->d_o) & 7) || (a->o_stride_s & 3) ||
-      (a->o_stride_h & 3) || (a->o_stride_b & 3) || (a->do_stride_s & 3) || (a->do_stride_h & 3) || (a->do_stride_b & 3))
-    return set_error(HB_ERR_ALIGN, "hb_fa_bwd_preprocess: o and d_o need 8-byte aligned rows");
+  if ((reinterpret_cast<uintptr_t>(a->o) & 15) || (reinterpret_cast<uintptr_t>(a->d_o) & 15) || (a->o_stride_s & 7) ||
+      (a->o_stride_h & 7) || (a->o_stride_b & 7) || (a->do_stride_s & 7) || (a->do_stride_h & 7) || (a->do_stride_b & 7))
+    return set_error(HB_ERR_ALIGN, "hb_fa_bwd_preprocess: o and d_o need 16-byte aligned rows");
   DeviceState* st = nullptr;
   rc = get_device_state(&st);
   if (rc != HB_OK) return rc;
   const long long rows = (long long)a->B * a->Hq * a->Sq;
-  const unsigned grid = (unsigned)((rows + 7) / 8);
+  const unsigned grid = (unsigned)((rows + 63) / 64);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   if (a->dtype == HB_BF16)
     fa_bwd_preprocess_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
@@ -705,10 +989,13 @@ extern "C" int hb_fa_bwd_dkdv(const hb_fa_bwd_args* a) {
   const long long total = (long long)a->B * a->Hkv * p.nkb;
   if (total > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_bwd_dkdv: problem too large");
   p.total_items = (int)total;
-  const int grid = (int)std::min<long long>(total, st->sm_count);
+  int grid = (int)std::min<long long>(total, st->sm_count);
+#ifdef HB_DEBUG_GRID_ENV  // measurement builds only: fewer CTAs than SMs
+  if (const char* e = getenv("HB_GRID")) grid = std::max(1, std::min(grid, atoi(e)));
+#endif
   static bool cfg_bf16[64] = {}, cfg_f16[64] = {};
-  if (a->dtype == HB_BF16) return bwd_launch(fa_bwd_dkdv_kernel<__nv_bfloat16>, p, grid, st, stream, cfg_bf16);
-  return bwd_launch(fa_bwd_dkdv_kernel<__half>, p, grid, st, stream, cfg_f16);
+  if (a->dtype == HB_BF16) return bwd_launch<BwdSmemKv>(fa_bwd_dkdv_kernel<__nv_bfloat16>, p, grid, st, stream, cfg_bf16);
+  return bwd_launch<BwdSmemKv>(fa_bwd_dkdv_kernel<__half>, p, grid, st, stream, cfg_f16);
 }
 
 extern "C" int hb_fa_bwd_dq(const hb_fa_bwd_args* a) {
@@ -735,8 +1022,17 @@ extern "C" int hb_fa_bwd_dq(const hb_fa_bwd_args* a) {
   const long long total = (long long)a->B * a->Hq * p.nqb;
   if (total > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_bwd_dq: problem too large");
   p.total_items = (int)total;
-  const int grid = (int)std::min<long long>(total, st->sm_count);
+  int grid = (int)std::min<long long>(total, st->sm_count);
+#ifdef HB_DEBUG_GRID_ENV  // measurement builds only: fewer CTAs than SMs
+  if (const char* e = getenv("HB_GRID")) grid = std::max(1, std::min(grid, atoi(e)));
+#endif
   static bool cfg_bf16[64] = {}, cfg_f16[64] = {};
-  if (a->dtype == HB_BF16) return bwd_launch(fa_bwd_dq_kernel<__nv_bfloat16>, p, grid, st, stream, cfg_bf16);
-  return bwd_launch(fa_bwd_dq_kernel<__half>, p, grid, st, stream, cfg_f16);
+  if (a->dtype == HB_BF16) return bwd_launch<BwdSmemQ>(fa_bwd_dq_kernel<__nv_bfloat16>, p, grid, st, stream, cfg_bf16);
+  return bwd_launch<BwdSmemQ>(fa_bwd_dq_kernel<__half>, p, grid, st, stream, cfg_f16);
 }
+
+#ifdef HB_BWD_PROF
+extern "C" int hb_debug_bwd_prof(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, hb::g_bwd_prof, sizeof(hb::g_bwd_prof)) == cudaSuccess ? 0 : 4;
+}
+#endif

@@ -2,6 +2,8 @@
 // FlashAttention-forward kernel; plus hb_debug_umma, a one-tile tcgen05 probe that
 // goes through the same descriptor helpers.
 #include "fa_fwd_sm100.cuh"
+
+#include <cstdlib>
 #include "host_common.h"
 
 #include <algorithm>
@@ -132,7 +134,10 @@ static int fa_fwd_impl(const hb_fa_args* a) {
     p.out_scale = vs / (FaTraits<__nv_fp8_e4m3>::kPScale * os);
   }
 
-  const int grid = (int)std::min<long long>(total, st->sm_count);
+  int grid = (int)std::min<long long>(total, st->sm_count);
+#ifdef HB_DEBUG_GRID_ENV  // measurement builds only: fewer CTAs than SMs, to see how the per-SM rate depends on the load on L2
+  if (const char* e = getenv("HB_GRID")) grid = std::max(1, std::min(grid, atoi(e)));
+#endif
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   if (a->dtype == HB_FP8_E4M3) return launch_fa<__nv_fp8_e4m3, 128>(p, grid, st->smem_optin, stream);
   if (a->dtype == HB_BF16) {
