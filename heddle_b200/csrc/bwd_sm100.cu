@@ -23,7 +23,7 @@
 //   dQ     tensor pipe:  S(0) dP(0) S(1) | dP(n+1) dQ(n) S(n+2) | ...
 //          S is double-buffered (S0, S1, dP, dQ = 512 columns) and dS(n) is written over S(n), so the
 //          dP region is free as soon as phase B(n) has read it and phase A(n+1) hides behind dP(n+1).
-// head_dim 128, bf16 / fp16.
+// head_dim 128 or 64, bf16 / fp16.
 #include "host_common.h"
 #include "ptx_sm100.cuh"
 
@@ -34,8 +34,7 @@
 namespace hb {
 
 constexpr int kBwdThreads = 320;
-constexpr int kBwdD = 128;
-constexpr uint32_t kBwdTileBytes = 128 * kBwdD * 2;  // one 128-row tile of a 16-bit tensor
+__host__ __device__ constexpr uint32_t bwd_tile_bytes(int d) { return 128u * static_cast<uint32_t>(d) * 2u; }  // one 128-row tile of a 16-bit tensor
 enum BwdRole : uint32_t { kBwdTma = 0x41, kBwdMma = 0x42, kBwdCons = 0x43, kBwdDrain = 0x44 };
 // Share of the exponentials evaluated on the FMA pipe instead of the MUFU: 0 none, 1 a quarter, 2 half.
 #ifndef HB_BWD_POLY
@@ -80,8 +79,9 @@ struct alignas(64) BwdParams {
 };
 
 // rings: A feeds the score product and the last product of the step, B the dP product (and dV)
-template <int kStagesA, int kStagesB, bool kStage>
+template <int D, int kStagesA, int kStagesB, bool kStage>
 struct BwdSmem {
+  static constexpr uint32_t kBwdTileBytes = bwd_tile_bytes(D);
   static constexpr int kSA = kStagesA, kSB = kStagesB;
   alignas(1024) uint8_t fixed[2][kBwdTileBytes];        // dkdv: K, V of the item;  dq: Q, dO of the item
   alignas(1024) uint8_t ring_a[kStagesA][kBwdTileBytes];  // dkdv: Q tiles;  dq: K tiles
@@ -104,8 +104,10 @@ struct BwdSmem {
   // dkdv: per consumer warp, double-buffered {-LSE*log2e, delta} of a query tile
   alignas(16) float stage[kStage ? 8 : 1][2][2][kStage ? 64 : 4];
 };
-using BwdSmemKv = BwdSmem<2, 2, true>;
-using BwdSmemQ = BwdSmem<3, 2, false>;
+template <int D>
+using BwdSmemKv = BwdSmem<D, 2, 2, true>;
+template <int D>
+using BwdSmemQ = BwdSmem<D, 3, 2, false>;
 
 // Shared-memory descriptor pieces (same conventions as the forward kernel)
 constexpr uint32_t kBwdDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -115,20 +117,20 @@ constexpr uint32_t kBwdLboMn = kBwdSub16 << 16;     // MN-major operand: next 64
 __device__ __forceinline__ uint64_t bwd_desc(uint32_t lo) { return (static_cast<uint64_t>(kBwdDescHi) << 32) | lo; }
 
 // D[128 x 128] = A[128 x head_dim] . B[128 x head_dim]^T, both operands K-major tiles in smem
-template <typename T>
+template <typename T, int D>
 __device__ __forceinline__ void bwd_mma_kk(uint32_t d_tmem, const void* a_tile, const void* b_tile) {
   constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, 128, 128, 0, 0);
   const uint32_t a_lo = (smem_u32(a_tile) >> 4) | kBwdLboK, b_lo = (smem_u32(b_tile) >> 4) | kBwdLboK;
 #pragma unroll
-  for (int kk = 0; kk < kBwdD / 16; ++kk) {
+  for (int kk = 0; kk < D / 16; ++kk) {
     const uint32_t off = static_cast<uint32_t>(kk >> 2) * kBwdSub16 + static_cast<uint32_t>(kk & 3) * 2u;
     umma_ss_f16(d_tmem, bwd_desc(a_lo + off), bwd_desc(b_lo + off), idesc, kk > 0 ? 1u : 0u);
   }
 }
 // D[128 x head_dim] (+)= A[128 x 128] (packed 16-bit, in TMEM) . B[128(K) x head_dim] (a row tile in smem, MN-major)
-template <typename T>
+template <typename T, int D>
 __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, const void* b_tile, uint32_t accumulate) {
-  constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, 128, kBwdD, 0, 1);
+  constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, 128, D, 0, 1);
   const uint32_t b_lo = (smem_u32(b_tile) >> 4) | kBwdLboMn;
 #pragma unroll
   for (int kk = 0; kk < 128 / 16; ++kk) {
@@ -137,10 +139,11 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, con
   }
 }
 
+template <int D>
 __device__ __forceinline__ void bwd_load_tile(void* dst, const CUtensorMap* tm, uint64_t* bar, int row0, int h, int b) {
-  mbar_arrive_expect_tx(bar, kBwdTileBytes);
+  mbar_arrive_expect_tx(bar, bwd_tile_bytes(D));
 #pragma unroll
-  for (int hh = 0; hh < kBwdD / 64; ++hh)
+  for (int hh = 0; hh < D / 64; ++hh)
     tma_load_4d(static_cast<uint8_t*>(dst) + hh * (128 * 128), tm, bar, hh * 64, row0, h, b);
 }
 
@@ -215,10 +218,11 @@ __device__ __forceinline__ void bwd_init(Smem& s, const AbortCtx& ctx, const voi
 // dK, dV: one CTA per (batch, kv head, 128-key tile); loops over the group's query heads and the
 // query tiles that can see the key tile.  TMEM: S^T [0,128) dP^T [128,256) dV [256,384) dK [384,512).
 // ------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  using Smem = BwdSmemKv;
+  using Smem = BwdSmemKv<D>;
+  constexpr uint32_t kBwdTileBytes = bwd_tile_bytes(D);
   Smem& s = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{&s.abort_flag, p.status};
@@ -262,7 +266,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
         f_phase ^= 1;
         mbar_arrive_expect_tx(&s.fixed_full, 2 * kBwdTileBytes);
 #pragma unroll
-        for (int hh = 0; hh < kBwdD / 64; ++hh) {
+        for (int hh = 0; hh < D / 64; ++hh) {
           tma_load_4d(s.fixed[0] + hh * (128 * 128), &p.tm_k, &s.fixed_full, hh * 64, k0, hkv, b);
           tma_load_4d(s.fixed[1] + hh * (128 * 128), &p.tm_v, &s.fixed_full, hh * 64, k0, hkv, b);
         }
@@ -274,12 +278,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
               ok = false;
               break;
             }
-            bwd_load_tile(s.ring_a[st], &p.tm_q, &s.a_full[st], qt * 128, hq, b);
+            bwd_load_tile<D>(s.ring_a[st], &p.tm_q, &s.a_full[st], qt * 128, hq, b);
             if (!mbar_wait(&s.b_empty[st], ph, ctx, kBwdTma)) {
               ok = false;
               break;
             }
-            bwd_load_tile(s.ring_b[st], &p.tm_do, &s.b_full[st], qt * 128, hq, b);
+            bwd_load_tile<D>(s.ring_b[st], &p.tm_do, &s.b_full[st], qt * 128, hq, b);
           }
         }
       }
@@ -304,14 +308,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
         if (!full_a(cnt)) break;
         tc_fence_after();
         if (leader) {
-          bwd_mma_kk<T>(tmem + 0, s.fixed[0], s.ring_a[cnt & 1u]);  // S^T = K Q^T
+          bwd_mma_kk<T, D>(tmem + 0, s.fixed[0], s.ring_a[cnt & 1u]);  // S^T = K Q^T
           umma_commit(&s.s_full[0]);
         }
         __syncwarp();
         if (!full_b(cnt)) break;
         tc_fence_after();
         if (leader) {
-          bwd_mma_kk<T>(tmem + 128, s.fixed[1], s.ring_b[cnt & 1u]);  // dP^T = V dO^T
+          bwd_mma_kk<T, D>(tmem + 128, s.fixed[1], s.ring_b[cnt & 1u]);  // dP^T = V dO^T
           umma_commit(&s.dp_full);
         }
         __syncwarp();
@@ -331,7 +335,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
           BWD_PROF(1)
           tc_fence_after();
           if (leader) {
-            bwd_mma_ts<T>(tmem + 256, tmem + 0, s.ring_b[st], n > 0 ? 1u : 0u);  // dV += P^T dO
+            bwd_mma_ts<T, D>(tmem + 256, tmem + 0, s.ring_b[st], n > 0 ? 1u : 0u);  // dV += P^T dO
             umma_commit(&s.b_empty[st]);
           }
           __syncwarp();
@@ -345,7 +349,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
             BWD_PROF(3)
             tc_fence_after();
             if (leader) {
-              bwd_mma_kk<T>(tmem + 0, s.fixed[0], s.ring_a[nx]);  // S^T of the next step, over P^T
+              bwd_mma_kk<T, D>(tmem + 0, s.fixed[0], s.ring_a[nx]);  // S^T of the next step, over P^T
               umma_commit(&s.s_full[0]);
             }
             __syncwarp();
@@ -362,10 +366,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
           BWD_PROF(5)
           tc_fence_after();
           if (leader) {
-            bwd_mma_ts<T>(tmem + 384, tmem + 128, s.ring_a[st], n > 0 ? 1u : 0u);  // dK += dS^T Q
+            bwd_mma_ts<T, D>(tmem + 384, tmem + 128, s.ring_a[st], n > 0 ? 1u : 0u);  // dK += dS^T Q
             umma_commit(&s.a_empty[st]);
             if (more) {
-              bwd_mma_kk<T>(tmem + 128, s.fixed[1], s.ring_b[nx]);  // dP^T of the next step, over dS^T
+              bwd_mma_kk<T, D>(tmem + 128, s.fixed[1], s.ring_b[nx]);  // dP^T of the next step, over dS^T
               umma_commit(&s.dp_full);
             }
           }
@@ -508,21 +512,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
         }
       }
       if (!ok) break;
-      // read-out: dV as is, dK times the softmax scale; each thread stores its 64 columns of the row
+      // read-out: dV as is, dK times the softmax scale; each thread stores its half of the row's head_dim columns
       if (!mbar_wait_warp(&s.acc_full, items & 1u, ctx, kBwdCons)) break;
       tc_fence_after();
       const bool live = key < p.Skv;
-      T* dv_row = static_cast<T*>(p.dv) + ((static_cast<long long>(b) * p.Hkv + hkv) * p.Skv + key) * kBwdD + col_in;
-      T* dk_row = static_cast<T*>(p.dk) + ((static_cast<long long>(b) * p.Hkv + hkv) * p.Skv + key) * kBwdD + col_in;
+      const uint32_t col_acc = static_cast<uint32_t>(half * (D / 2));
+      T* dv_row = static_cast<T*>(p.dv) + ((static_cast<long long>(b) * p.Hkv + hkv) * p.Skv + key) * D + col_acc;
+      T* dk_row = static_cast<T*>(p.dk) + ((static_cast<long long>(b) * p.Hkv + hkv) * p.Skv + key) * D + col_acc;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
         __syncwarp();
-        tmem_ld32(tmem + lane_off + 256 + col_in + c * 32, r);
+        tmem_ld32(tmem + lane_off + 256 + col_acc + c * 32, r);
         tmem_wait_ld();
         if (live) bwd_store_row<T>(dv_row + c * 32, r, 1.0f);
         __syncwarp();
-        tmem_ld32(tmem + lane_off + 384 + col_in + c * 32, r);
+        tmem_ld32(tmem + lane_off + 384 + col_acc + c * 32, r);
         tmem_wait_ld();
         if (live) bwd_store_row<T>(dk_row + c * 32, r, p.scale);
       }
@@ -544,10 +549,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
 // dQ: one CTA per (batch, query head, 128-query tile); loops over the key tiles the queries see.
 // TMEM: S buffers [0,128) [128,256), dP [256,384), dQ [384,512).
 // ------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  using Smem = BwdSmemQ;
+  using Smem = BwdSmemQ<D>;
+  constexpr uint32_t kBwdTileBytes = bwd_tile_bytes(D);
   Smem& s = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{&s.abort_flag, p.status};
@@ -592,7 +598,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
         f_phase ^= 1;
         mbar_arrive_expect_tx(&s.fixed_full, 2 * kBwdTileBytes);
 #pragma unroll
-        for (int hh = 0; hh < kBwdD / 64; ++hh) {
+        for (int hh = 0; hh < D / 64; ++hh) {
           tma_load_4d(s.fixed[0] + hh * (128 * 128), &p.tm_q, &s.fixed_full, hh * 64, q0, hq, b);
           tma_load_4d(s.fixed[1] + hh * (128 * 128), &p.tm_do, &s.fixed_full, hh * 64, q0, hq, b);
         }
@@ -603,12 +609,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
             ok = false;
             break;
           }
-          bwd_load_tile(s.ring_a[sa], &p.tm_k, &s.a_full[sa], kt * 128, hkv, b);
+          bwd_load_tile<D>(s.ring_a[sa], &p.tm_k, &s.a_full[sa], kt * 128, hkv, b);
           if (!mbar_wait(&s.b_empty[sb], pb, ctx, kBwdTma)) {
             ok = false;
             break;
           }
-          bwd_load_tile(s.ring_b[sb], &p.tm_v, &s.b_full[sb], kt * 128, hkv, b);
+          bwd_load_tile<D>(s.ring_b[sb], &p.tm_v, &s.b_full[sb], kt * 128, hkv, b);
         }
       }
     }
@@ -625,7 +631,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
         if (!mbar_wait_warp(&s.a_full[c % 3u], (c / 3u) & 1u, ctx, kBwdMma)) return false;
         tc_fence_after();
         if (leader) {
-          bwd_mma_kk<T>(tmem + (c & 1u) * 128u, s.fixed[0], s.ring_a[c % 3u]);
+          bwd_mma_kk<T, D>(tmem + (c & 1u) * 128u, s.fixed[0], s.ring_a[c % 3u]);
           umma_commit(&s.s_full[c & 1u]);
         }
         __syncwarp();
@@ -636,7 +642,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
         if (!mbar_wait_warp(&s.b_full[c & 1u], (c >> 1) & 1u, ctx, kBwdMma)) return false;
         tc_fence_after();
         if (leader) {
-          bwd_mma_kk<T>(tmem + 256, s.fixed[1], s.ring_b[c & 1u]);
+          bwd_mma_kk<T, D>(tmem + 256, s.fixed[1], s.ring_b[c & 1u]);
           umma_commit(&s.dp_full);
           umma_commit(&s.b_empty[c & 1u]);
         }
@@ -670,11 +676,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
             // dP of the step has been read and dS written over S: the next dP goes first, phase B of the
             // next step waits for it
             if (n + 1 < nk) {
-              bwd_mma_kk<T>(tmem + 256, s.fixed[1], s.ring_b[(cnt + 1) & 1u]);
+              bwd_mma_kk<T, D>(tmem + 256, s.fixed[1], s.ring_b[(cnt + 1) & 1u]);
               umma_commit(&s.dp_full);
               umma_commit(&s.b_empty[(cnt + 1) & 1u]);
             }
-            bwd_mma_ts<T>(tmem + 384, tmem + (cnt & 1u) * 128u, s.ring_a[cnt % 3u], n > 0 ? 1u : 0u);  // dQ += dS K
+            bwd_mma_ts<T, D>(tmem + 384, tmem + (cnt & 1u) * 128u, s.ring_a[cnt % 3u], n > 0 ? 1u : 0u);  // dQ += dS K
             umma_commit(&s.a_empty[cnt % 3u]);
           }
           __syncwarp();
@@ -797,12 +803,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
       if (!ok) break;
       if (!mbar_wait_warp(&s.acc_full, items & 1u, ctx, kBwdCons)) break;
       tc_fence_after();
-      T* dq_row = static_cast<T*>(p.dq) + stat * kBwdD + col_in;
+      const uint32_t col_acc = static_cast<uint32_t>(half * (D / 2));
+      T* dq_row = static_cast<T*>(p.dq) + stat * D + col_acc;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
         __syncwarp();
-        tmem_ld32(tmem + lane_off + 384 + col_in + c * 32, r);
+        tmem_ld32(tmem + lane_off + 384 + col_acc + c * 32, r);
         tmem_wait_ld();
         if (live) bwd_store_row<T>(dq_row + c * 32, r, p.scale);
       }
@@ -823,29 +830,30 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
 }
 
 // ------------------------------------------------------------------------------------------
-// delta = rowsum(O o dO): HBM-bound (reads 2 x 256 B per row, writes 4 B).  Sixteen lanes share a row
-// (16 bytes each), a warp covers eight rows with all eight 16-byte loads of a lane in flight at once.
+// delta = rowsum(O o dO): HBM-bound (reads 2 x 2 D bytes per row, writes 4 B).  D / 8 lanes share a row
+// (16 bytes each); a warp covers 4 * 256 / D rows with all eight 16-byte loads of a lane in flight at once.
 // ------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(256) fa_bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
                                                                  float* __restrict__ delta, int B, int H, int S,
                                                                  long long o_sb, long long o_sh, long long o_ss,
                                                                  long long g_sb, long long g_sh, long long g_ss) {
-  const int lane = threadIdx.x & 31, sub = lane >> 4, l16 = lane & 15;
+  constexpr int kLanesPerRow = D / 8, kRowsPerLoad = 32 / kLanesPerRow, kRowsPerWarp = 4 * kRowsPerLoad;
+  const int lane = threadIdx.x & 31, sub = lane / kLanesPerRow, lr = lane % kLanesPerRow;
   const long long total = static_cast<long long>(B) * H * S;
-  const long long row0 = (blockIdx.x * 8ll + (threadIdx.x >> 5)) * 8;
+  const long long row0 = (blockIdx.x * 8ll + (threadIdx.x >> 5)) * kRowsPerWarp;
   uint4 a[4], g[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const long long row = row0 + i * 2 + sub;
+    const long long row = row0 + i * kRowsPerLoad + sub;
     a[i] = make_uint4(0u, 0u, 0u, 0u);
     g[i] = a[i];
     if (row < total) {
       const int sq = static_cast<int>(row % S);
       const long long bh = row / S;
       const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
-      a[i] = *reinterpret_cast<const uint4*>(o + b * o_sb + h * o_sh + sq * o_ss + l16 * 8);
-      g[i] = *reinterpret_cast<const uint4*>(d_o + b * g_sb + h * g_sh + sq * g_ss + l16 * 8);
+      a[i] = *reinterpret_cast<const uint4*>(o + b * o_sb + h * o_sh + sq * o_ss + lr * 8);
+      g[i] = *reinterpret_cast<const uint4*>(d_o + b * g_sb + h * g_sh + sq * g_ss + lr * 8);
     }
   }
 #pragma unroll
@@ -856,9 +864,9 @@ __global__ void __launch_bounds__(256) fa_bwd_preprocess_kernel(const T* __restr
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc = fmaf(static_cast<float>(ap[e]), static_cast<float>(gp[e]), acc);
 #pragma unroll
-    for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    const long long row = row0 + i * 2 + sub;
-    if (l16 == 0 && row < total) delta[row] = acc;
+    for (int off = kLanesPerRow / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    const long long row = row0 + i * kRowsPerLoad + sub;
+    if (lr == 0 && row < total) delta[row] = acc;
   }
 }
 
@@ -871,7 +879,7 @@ static int bwd_check(const hb_fa_bwd_args* a, const char* who) {
     return set_error(HB_ERR_BAD_ARG, "%s: negative or zero extent", who);
   if (a->Hq % a->Hkv != 0) return set_error(HB_ERR_BAD_ARG, "%s: Hq is not a multiple of Hkv", who);
   if (a->dtype != HB_BF16 && a->dtype != HB_FP16) return set_error(HB_ERR_UNSUPPORTED, "%s: dtype %d not supported (bf16, fp16)", who, a->dtype);
-  if (a->D != kBwdD) return set_error(HB_ERR_UNSUPPORTED, "%s: head_dim %d not supported (128)", who, a->D);
+  if (a->D != 128 && a->D != 64) return set_error(HB_ERR_UNSUPPORTED, "%s: head_dim %d not supported (64, 128)", who, a->D);
   if (a->causal && a->Skv < a->Sq) return set_error(HB_ERR_UNSUPPORTED, "%s: causal needs Skv >= Sq", who);
   return HB_OK;
 }
@@ -917,8 +925,9 @@ static int bwd_fill(const hb_fa_bwd_args* a, BwdParams& p, const DeviceState* st
   return HB_OK;
 }
 
-template <typename Smem, typename K>
-static int bwd_launch(K kernel, const BwdParams& p, int grid, const DeviceState* st, cudaStream_t stream, bool* configured) {
+template <typename Smem>
+static int bwd_launch(void (*kernel)(const BwdParams), const BwdParams& p, int grid, const DeviceState* st,
+                      cudaStream_t stream, bool* configured) {
   if ((int)sizeof(Smem) > st->smem_optin)
     return set_error(HB_ERR_UNSUPPORTED, "attention backward needs %d bytes of shared memory per CTA, the device offers %d",
                      (int)sizeof(Smem), st->smem_optin);
@@ -927,6 +936,27 @@ static int bwd_launch(K kernel, const BwdParams& p, int grid, const DeviceState*
     configured[st->device & 63] = true;
   }
   kernel<<<grid, kBwdThreads, sizeof(Smem), stream>>>(p);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB_OK;
+}
+template <typename T, int D>
+static int launch_dkdv(const BwdParams& p, int grid, const DeviceState* st, cudaStream_t stream) {
+  static bool configured[64] = {};
+  return bwd_launch<BwdSmemKv<D>>(fa_bwd_dkdv_kernel<T, D>, p, grid, st, stream, configured);
+}
+template <typename T, int D>
+static int launch_dq(const BwdParams& p, int grid, const DeviceState* st, cudaStream_t stream) {
+  static bool configured[64] = {};
+  return bwd_launch<BwdSmemQ<D>>(fa_bwd_dq_kernel<T, D>, p, grid, st, stream, configured);
+}
+template <typename T, int D>
+static int launch_preprocess(const hb_fa_bwd_args* a, cudaStream_t stream) {
+  constexpr int kRowsPerBlock = 8 * 4 * (32 / (D / 8));
+  const long long rows = (long long)a->B * a->Hq * a->Sq;
+  const unsigned grid = (unsigned)((rows + kRowsPerBlock - 1) / kRowsPerBlock);
+  fa_bwd_preprocess_kernel<T, D><<<grid, 256, 0, stream>>>(static_cast<const T*>(a->o), static_cast<const T*>(a->d_o), a->delta,
+                                                          a->B, a->Hq, a->Sq, a->o_stride_b, a->o_stride_h, a->o_stride_s,
+                                                          a->do_stride_b, a->do_stride_h, a->do_stride_s);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB_OK;
 }
@@ -947,19 +977,10 @@ extern "C" int hb_fa_bwd_preprocess(const hb_fa_bwd_args* a) {
   DeviceState* st = nullptr;
   rc = get_device_state(&st);
   if (rc != HB_OK) return rc;
-  const long long rows = (long long)a->B * a->Hq * a->Sq;
-  const unsigned grid = (unsigned)((rows + 63) / 64);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   if (a->dtype == HB_BF16)
-    fa_bwd_preprocess_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(a->o), static_cast<const __nv_bfloat16*>(a->d_o), a->delta, a->B, a->Hq, a->Sq,
-        a->o_stride_b, a->o_stride_h, a->o_stride_s, a->do_stride_b, a->do_stride_h, a->do_stride_s);
-  else
-    fa_bwd_preprocess_kernel<__half><<<grid, 256, 0, stream>>>(
-        static_cast<const __half*>(a->o), static_cast<const __half*>(a->d_o), a->delta, a->B, a->Hq, a->Sq, a->o_stride_b,
-        a->o_stride_h, a->o_stride_s, a->do_stride_b, a->do_stride_h, a->do_stride_s);
-  HB_CUDA_CHECK(cudaGetLastError());
-  return HB_OK;
+    return a->D == 128 ? launch_preprocess<__nv_bfloat16, 128>(a, stream) : launch_preprocess<__nv_bfloat16, 64>(a, stream);
+  return a->D == 128 ? launch_preprocess<__half, 128>(a, stream) : launch_preprocess<__half, 64>(a, stream);
 }
 
 extern "C" int hb_fa_bwd_dkdv(const hb_fa_bwd_args* a) {
@@ -993,9 +1014,9 @@ extern "C" int hb_fa_bwd_dkdv(const hb_fa_bwd_args* a) {
 #ifdef HB_DEBUG_GRID_ENV  // measurement builds only: fewer CTAs than SMs
   if (const char* e = getenv("HB_GRID")) grid = std::max(1, std::min(grid, atoi(e)));
 #endif
-  static bool cfg_bf16[64] = {}, cfg_f16[64] = {};
-  if (a->dtype == HB_BF16) return bwd_launch<BwdSmemKv>(fa_bwd_dkdv_kernel<__nv_bfloat16>, p, grid, st, stream, cfg_bf16);
-  return bwd_launch<BwdSmemKv>(fa_bwd_dkdv_kernel<__half>, p, grid, st, stream, cfg_f16);
+  if (a->dtype == HB_BF16)
+    return a->D == 128 ? launch_dkdv<__nv_bfloat16, 128>(p, grid, st, stream) : launch_dkdv<__nv_bfloat16, 64>(p, grid, st, stream);
+  return a->D == 128 ? launch_dkdv<__half, 128>(p, grid, st, stream) : launch_dkdv<__half, 64>(p, grid, st, stream);
 }
 
 extern "C" int hb_fa_bwd_dq(const hb_fa_bwd_args* a) {
@@ -1026,9 +1047,9 @@ extern "C" int hb_fa_bwd_dq(const hb_fa_bwd_args* a) {
 #ifdef HB_DEBUG_GRID_ENV  // measurement builds only: fewer CTAs than SMs
   if (const char* e = getenv("HB_GRID")) grid = std::max(1, std::min(grid, atoi(e)));
 #endif
-  static bool cfg_bf16[64] = {}, cfg_f16[64] = {};
-  if (a->dtype == HB_BF16) return bwd_launch<BwdSmemQ>(fa_bwd_dq_kernel<__nv_bfloat16>, p, grid, st, stream, cfg_bf16);
-  return bwd_launch<BwdSmemQ>(fa_bwd_dq_kernel<__half>, p, grid, st, stream, cfg_f16);
+  if (a->dtype == HB_BF16)
+    return a->D == 128 ? launch_dq<__nv_bfloat16, 128>(p, grid, st, stream) : launch_dq<__nv_bfloat16, 64>(p, grid, st, stream);
+  return a->D == 128 ? launch_dq<__half, 128>(p, grid, st, stream) : launch_dq<__half, 64>(p, grid, st, stream);
 }
 
 #ifdef HB_BWD_PROF

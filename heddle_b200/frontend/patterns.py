@@ -51,7 +51,7 @@ class TileLangFlashAttnFunc(torch.autograd.Function):
     The reference's Function is forward only; its backward is sketched as the separated
     preprocess / dK,dV / dQ kernels (bwd_separator.py:366-455, with ``backward`` saving
     Q, K, V, O, LSE at :399-405).  That split is what ``backward`` runs here: when a gradient is
-    needed the forward keeps the LSE, and head_dim 128 in bf16 / fp16 is required."""
+    needed the forward keeps the LSE, and head_dim 64 or 128 in bf16 / fp16 is required."""
 
     @staticmethod
     def forward(ctx, q, k, v, scale=None):

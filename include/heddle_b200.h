@@ -239,7 +239,7 @@ int hb_prepare_weight(const hb_prepare_args* args);
  * 16-byte aligned rows), lse is the natural-log LSE that hb_fa_fwd writes, lse and delta are
  * [B, Hq, Sq] fp32 contiguous.  Outputs are contiguous: dq [B, Hq, Sq, D], dk and dv
  * [B, Hkv, Skv, D] (with grouped queries a kv head's gradient is the sum over its query heads,
- * formed inside the one CTA that owns the key tile).  bf16 / fp16, D = 128, causal mask aligned
+ * formed inside the one CTA that owns the key tile).  bf16 / fp16, D in {64, 128}, causal mask aligned
  * to the end of the keys (key <= query + Skv - Sq) as in hb_fa_fwd.
  *   hb_fa_bwd_preprocess reads o, d_o            and writes delta
  *   hb_fa_bwd_dkdv       reads q, k, v, d_o, lse, delta and writes dk, dv

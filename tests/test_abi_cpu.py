@@ -98,8 +98,8 @@ def test_argument_validation_needs_no_gpu(built_lib):
     for fn in (built_lib.hb_fa_bwd_preprocess, built_lib.hb_fa_bwd_dkdv, built_lib.hb_fa_bwd_dq):
         assert fn(None) == _lib.HB_ERR_BAD_ARG
         g = _lib.FaBwdArgs()
-        g.B, g.Hq, g.Hkv, g.Sq, g.Skv, g.D, g.dtype = 1, 4, 4, 128, 128, 64, _lib.HB_BF16
-        assert fn(ctypes.byref(g)) == _lib.HB_ERR_UNSUPPORTED  # head_dim 128 only
+        g.B, g.Hq, g.Hkv, g.Sq, g.Skv, g.D, g.dtype = 1, 4, 4, 128, 128, 96, _lib.HB_BF16
+        assert fn(ctypes.byref(g)) == _lib.HB_ERR_UNSUPPORTED  # head_dim 64 or 128
         assert b"head_dim" in built_lib.hb_last_error()
         g.D, g.dtype = 128, _lib.HB_FP8_E4M3
         assert fn(ctypes.byref(g)) == _lib.HB_ERR_UNSUPPORTED  # 16-bit types only

@@ -43,9 +43,9 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,causal,dtype", CASES)
-def test_backward_matches_oracle(ops, B, Hq, Hkv, Sq, Skv, causal, dtype):
-    D = 128
+def test_backward_matches_oracle(ops, B, Hq, Hkv, Sq, Skv, causal, dtype, D):
     q, k, v = O.make_qkv(B, Hq, Hkv, Sq, Skv, D, seed=Sq + Skv, dtype=dtype)
     d_o = _grad_out(B, Hq, Sq, D, 5 + Sq, dtype)
     qc, kc, vc, gc = q.cuda(), k.cuda(), v.cuda(), d_o.cuda()
@@ -137,8 +137,8 @@ def test_backward_empty_and_rejected_inputs(ops):
     lse = torch.zeros(1, 2, 0, dtype=torch.float32, device="cuda")
     dq, dk, dv = ops.fa_bwd(q, k, k, q, q, lse)
     assert dq.shape == q.shape and dk.abs().max().item() == 0.0 and dv.abs().max().item() == 0.0
-    q64 = torch.zeros(1, 2, 64, 64, dtype=torch.bfloat16, device="cuda")
+    q96 = torch.zeros(1, 2, 64, 96, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(HeddleError, match="head_dim"):
-        ops.fa_bwd(q64, q64, q64, q64, q64, torch.zeros(1, 2, 64, device="cuda"))
+        ops.fa_bwd(q96, q96, q96, q96, q96, torch.zeros(1, 2, 64, device="cuda"))
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         ops.fa_bwd_preprocess(torch.zeros(1, 1, 8, 128, dtype=torch.bfloat16), torch.zeros(1, 1, 8, 128, dtype=torch.bfloat16))
