@@ -48,6 +48,25 @@ log = logging.getLogger("heddle_b200")
 # ----------------------------------------------------------------------------------------
 # leaves inserted into FX graphs
 # ----------------------------------------------------------------------------------------
+class _SdpaFunc(torch.autograd.Function):
+    """Differentiable route of ``_tilelang_sdpa_direct``: the forward keeps the LSE, the backward is the
+    separated preprocess / dK,dV / dQ kernels (the split sketched in
+    Heddle/heddle/frontend/bwd_separator.py:366-455; the reference's leaf is forward only)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale, out):
+        o, lse = ops.fa_fwd(q, k, v, causal=causal, softmax_scale=scale, out=out, return_lse=True)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ops.fa_bwd(q, k, v, o, grad_out, lse, causal=ctx.causal, softmax_scale=ctx.scale)
+        return dq, dk, dv, None, None, None
+
+
 @torch.fx.wrap
 def _tilelang_sdpa_direct(q, k, v, is_causal=None, scale=None, out_bshd=False):
     """Attention on (B, H, S, D) tensors; returns a new (B, H, Sq, D) tensor of q's dtype.
@@ -67,6 +86,8 @@ def _tilelang_sdpa_direct(q, k, v, is_causal=None, scale=None, out_bshd=False):
         out_dtype = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16
         out = torch.empty((q.shape[0], q.shape[2], q.shape[1], q.shape[3]), dtype=out_dtype,
                           device=q.device).transpose(1, 2)
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return _SdpaFunc.apply(q, k, v, bool(is_causal), scale, out)
     return ops.fa_fwd(q, k, v, causal=bool(is_causal), softmax_scale=scale, out=out)
 
 
@@ -385,6 +406,8 @@ def tilelang_backend(gm: torch.fx.GraphModule, example_inputs: List[torch.Tensor
     2. GEMM + epilogue fusion of what surrounds it (linear + activation, SwiGLU,
        RMSNorm-folded linears, RoPE on the QKV projection) onto the tcgen05 GEMM;
     3. returns the rewritten ``GraphModule``.
+
+    Step 2 is for inference graphs; when parameters or inputs require gradients only step 1 runs.
     """
     enable_h2o = _env_flag("TILELANG_FRONTEND_ENABLE_H2O_FUSE", "1")
     enable_fa = _env_flag("TILELANG_FRONTEND_ENABLE_FLASHATTN_PATTERN", "1")
@@ -409,7 +432,15 @@ def tilelang_backend(gm: torch.fx.GraphModule, example_inputs: List[torch.Tensor
     if fused_attention:
         _prefer_bshd_outputs(gm)
 
-    if enable_gemm and (continue_after or not fused_attention):
+    # The fused GEMM leaves are forward-only (as the reference's generated GEMM partitions are): in a graph
+    # captured for training the linear layers stay PyTorch ops, whose autograd provides their backward; the
+    # attention leaves carry their own backward kernels.
+    training = torch.is_grad_enabled() and (
+        any(p.requires_grad for p in gm.parameters())
+        or any(isinstance(t, torch.Tensor) and t.requires_grad for t in example_inputs))
+    if training and enable_gemm:
+        log.info("graph needs gradients: GEMM + epilogue fusion skipped")
+    if enable_gemm and not training and (continue_after or not fused_attention):
         from .fusion import fuse_gemm_epilogues
 
         n = fuse_gemm_epilogues(gm)

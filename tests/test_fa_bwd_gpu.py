@@ -142,3 +142,41 @@ def test_backward_empty_and_rejected_inputs(ops):
         ops.fa_bwd(q96, q96, q96, q96, q96, torch.zeros(1, 2, 64, device="cuda"))
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         ops.fa_bwd_preprocess(torch.zeros(1, 1, 8, 128, dtype=torch.bfloat16), torch.zeros(1, 1, 8, 128, dtype=torch.bfloat16))
+
+
+def test_training_step_through_the_compiled_backend(ops):
+    """torch.compile(backend=tilelang_backend) on a module that calls SDPA: the attention leaf is
+    differentiable, gradients of the projections match eager PyTorch in fp32."""
+    import heddle_b200 as heddle
+
+    class Attn(torch.nn.Module):
+        def __init__(self, hidden=256, heads=2):
+            super().__init__()
+            self.heads = heads
+            self.qkv = torch.nn.Linear(hidden, 3 * hidden, bias=False)
+            self.proj = torch.nn.Linear(hidden, hidden, bias=False)
+
+        def forward(self, x):
+            B, S, Hd = x.shape
+            q, k, v = self.qkv(x).view(B, S, 3, self.heads, Hd // self.heads).permute(2, 0, 3, 1, 4)
+            o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+            return self.proj(o.transpose(1, 2).reshape(B, S, Hd))
+
+    torch.manual_seed(0)
+    ref = Attn().float()
+    x = torch.randn(2, 256, 256)
+    ref(x).square().mean().backward()
+    model = Attn()
+    model.load_state_dict(ref.state_dict())
+    model = model.cuda().to(torch.bfloat16)
+    heddle.init()
+    torch._dynamo.reset()
+    compiled = torch.compile(model, backend=heddle.frontend.tilelang_backend)
+    loss = compiled(x.cuda().to(torch.bfloat16)).float().square().mean()
+    loss.backward()
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    for (name, p_ref), p_got in zip(ref.named_parameters(), model.parameters()):
+        assert p_got.grad is not None, name
+        err = (p_got.grad.float().cpu() - p_ref.grad).abs().max().item()
+        assert err <= 3e-2 * max(p_ref.grad.abs().max().item(), 1e-3), (name, err, p_ref.grad.abs().max().item())

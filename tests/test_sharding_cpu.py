@@ -64,7 +64,7 @@ def _worker(rank, world, port, fail_rank, out_dir):
         if status.item() == 0:
             dist.all_reduce(out)   # only to check the result; the data path itself has no collective
             ref, _ = O.attention_eager(q, k, v, causal=True)
-            ok = torch.allclose(out, ref, atol=1e-6)
+            ok = torch.allclose(out, ref, atol=2e-5)   # slices and the full problem may block their fp32 sums differently
         else:
             ok = False
         Path(out_dir, f"rank{rank}.txt").write_text(f"{int(status.item())} {int(ok)}")
