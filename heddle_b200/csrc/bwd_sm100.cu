@@ -74,7 +74,8 @@ struct alignas(64) BwdParams {
   int B, Hq, Hkv, Sq, Skv;
   int group, causal;
   int nkb, nqb;     // 128-row key / query tiles
-  int total_items;  // dkdv: B * Hkv * nkb;  dq: B * Hq * nqb
+  int npairs;       // pairs of tiles per head: dkdv ceil(nkb / 2), dq ceil(nqb / 2)
+  int total_items;  // pairs: dkdv B * Hkv * npairs;  dq B * Hq * npairs
   float scale_log2, scale;
 };
 
@@ -91,7 +92,7 @@ struct BwdSmem {
   uint64_t b_full[kStagesB], b_empty[kStagesB];
   uint64_t s_full[2];  // MMA -> consumers: scores are in TMEM (dkdv uses [0] only)
   uint64_t dp_full;    // MMA -> consumers: dP is in TMEM
-  uint64_t p_ready;    // consumers -> MMA: P written (dkdv only)
+  uint64_t p_ready[2]; // consumers -> MMA: first / second half of every warp's P columns written (dkdv only)
   uint64_t ds_ready;   // consumers -> MMA: dS written, dP read
   // warps 0-3 -> warps 4-7: columns [32,64) of a tile have been read (the upper warps' 16-bit results
   // land there).  One completion per step and barrier (dkdv: [0] scores, [1] dP; dq: [score buffer]),
@@ -136,6 +137,21 @@ __device__ __forceinline__ void bwd_mma_ts(uint32_t d_tmem, uint32_t a_tmem, con
   for (int kk = 0; kk < 128 / 16; ++kk) {
     umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), bwd_desc(b_lo + static_cast<uint32_t>(kk) * 128u), idesc,
                 kk > 0 ? 1u : accumulate);
+  }
+}
+
+// The same product restricted to the K-steps (16 rows of A's columns / B's rows each) named in kMask
+template <typename T, int D, uint32_t kMask>
+__device__ __forceinline__ void bwd_mma_ts_part(uint32_t d_tmem, uint32_t a_tmem, const void* b_tile, uint32_t accumulate) {
+  constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, 128, D, 0, 1);
+  const uint32_t b_lo = (smem_u32(b_tile) >> 4) | kBwdLboMn;
+  uint32_t acc = accumulate;
+#pragma unroll
+  for (int kk = 0; kk < 128 / 16; ++kk) {
+    if ((kMask >> kk) & 1u) {
+      umma_ts_f16(d_tmem, a_tmem + static_cast<uint32_t>(kk * 8), bwd_desc(b_lo + static_cast<uint32_t>(kk) * 128u), idesc, acc);
+      acc = 1u;
+    }
   }
 }
 
@@ -203,7 +219,8 @@ __device__ __forceinline__ void bwd_init(Smem& s, const AbortCtx& ctx, const voi
   mbar_init(&s.s_full[0], 1);
   mbar_init(&s.s_full[1], 1);
   mbar_init(&s.dp_full, 1);
-  mbar_init(&s.p_ready, 8);
+  mbar_init(&s.p_ready[0], 8);
+  mbar_init(&s.p_ready[1], 8);
   mbar_init(&s.ds_ready, 8);
   mbar_init(&s.half_read[0], 4);
   mbar_init(&s.half_read[1], 4);
@@ -244,14 +261,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
   const bool run = (s.abort_flag == 0);
   const int past = p.Skv - p.Sq;
 
-  auto item_of = [&](int g, int& b, int& hkv, int& k0, int& qt0) {
-    // heaviest key tiles (lowest index under a causal mask) first
-    const int kb = g % p.nkb;
-    const int bh = g / p.nkb;
+  // Work list: entry u >> 1 is a pair of key tiles (pair, nkb-1-pair) of one (batch, kv head), u & 1 selects
+  // the tile.  Under a causal mask the two tiles of a pair together see nqb + 1 query tiles whatever the pair, so
+  // the static round-robin over pairs keeps the persistent CTAs balanced.
+  auto item_of = [&](int u, int& b, int& hkv, int& k0, int& qt0) -> bool {
+    const int g = u >> 1;
+    const int pair = g % p.npairs;
+    const int bh = g / p.npairs;
+    const int kb = (u & 1) ? p.nkb - 1 - pair : pair;
+    if ((u & 1) && kb == pair) return false;  // middle tile of an odd count
     b = bh / p.Hkv;
     hkv = bh - b * p.Hkv;
     k0 = kb * 128;
     qt0 = p.causal ? max(0, (k0 - past) / 128) : 0;
+    return true;
   };
 
   if (warp == 8) {
@@ -259,9 +282,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
       // ---------------- TMA producer ----------------
       uint32_t cnt = 0, f_phase = 1;  // cnt: steps loaded so far (stage = cnt & 1 in both rings)
       bool ok = true;
-      for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x) {
+      for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1)) {
         int b, hkv, k0, qt0;
-        item_of(g, b, hkv, k0, qt0);
+        if (!item_of(u, b, hkv, k0, qt0)) continue;
         if (!mbar_wait(&s.fixed_empty, f_phase, ctx, kBwdTma)) break;
         f_phase ^= 1;
         mbar_arrive_expect_tx(&s.fixed_full, 2 * kBwdTileBytes);
@@ -298,9 +321,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
       BWD_PROF_DECL
       auto full_a = [&](uint32_t c) { return mbar_wait_warp(&s.a_full[c & 1u], (c >> 1) & 1u, ctx, kBwdMma); };
       auto full_b = [&](uint32_t c) { return mbar_wait_warp(&s.b_full[c & 1u], (c >> 1) & 1u, ctx, kBwdMma); };
-      for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x, ++items) {
+      for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1), ++items) {
         int b, hkv, k0, qt0;
-        item_of(g, b, hkv, k0, qt0);
+        if (!item_of(u, b, hkv, k0, qt0)) {
+          --items;  // not an item: keep the count of real items
+          continue;
+        }
         const int n_steps = p.group * (p.nqb - qt0);
         if (!mbar_wait_warp(&s.fixed_full, f_phase, ctx, kBwdMma)) break;
         f_phase ^= 1;
@@ -328,26 +354,34 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
             ok = false;
             break;
           }
-          if (!mbar_wait_warp(&s.p_ready, par, ctx, kBwdMma)) {
+          // dV += P^T dO in two parts: queries [0,32) and [64,96) of the tile (the first half of every
+          // consumer warp's columns) while the consumers are still working on the other half
+          if (!mbar_wait_warp(&s.p_ready[0], par, ctx, kBwdMma)) {
             ok = false;
             break;
           }
           BWD_PROF(1)
           tc_fence_after();
+          if (leader) bwd_mma_ts_part<T, D, 0x33u>(tmem + 256, tmem + 0, s.ring_b[st], n > 0 ? 1u : 0u);
+          __syncwarp();
+          // the Q tile of the next step was requested when dK of the previous step completed
+          if (more && !full_a(cnt + 1)) {
+            ok = false;
+            break;
+          }
+          BWD_PROF(3)
+          if (!mbar_wait_warp(&s.p_ready[1], par, ctx, kBwdMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
           if (leader) {
-            bwd_mma_ts<T, D>(tmem + 256, tmem + 0, s.ring_b[st], n > 0 ? 1u : 0u);  // dV += P^T dO
+            bwd_mma_ts_part<T, D, 0xCCu>(tmem + 256, tmem + 0, s.ring_b[st], 1u);
             umma_commit(&s.b_empty[st]);
           }
           __syncwarp();
           BWD_PROF(2)
           if (more) {
-            // the Q tile of the next step was requested when dK of the previous step completed
-            if (!full_a(cnt + 1)) {
-              ok = false;
-              break;
-            }
-            BWD_PROF(3)
-            tc_fence_after();
             if (leader) {
               bwd_mma_kk<T, D>(tmem + 0, s.fixed[0], s.ring_a[nx]);  // S^T of the next step, over P^T
               umma_commit(&s.s_full[0]);
@@ -400,9 +434,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
     const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
     uint32_t cnt = 0, items = 0;
     bool ok = true;
-    for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x, ++items) {
+    for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1), ++items) {
       int b, hkv, k0, qt0;
-      item_of(g, b, hkv, k0, qt0);
+      if (!item_of(u, b, hkv, k0, qt0)) {
+        --items;  // not an item: keep the count of real items
+        continue;
+      }
       const int key = k0 + key_in_tile;
       for (int hg = 0; ok && hg < p.group; ++hg) {
         const int hq = hkv * p.group + hg;
@@ -446,30 +483,35 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
             const bool need_mask = p.causal && (qt * 128 < k0 + 127 - past);
             const int q_min = key - past - qt * 128 - half * 64;  // first visible query, relative to this thread's columns
 #pragma unroll
-            for (int e = 0; e < 64; e += 4) {
-              bwd_exp4(&sv[e], e, sc2, nl4[e >> 2], &pr[e]);
-              if (need_mask) {
+            for (int h2 = 0; h2 < 2; ++h2) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) pr[e + u] = (e + u >= q_min) ? pr[e + u] : 0.f;
+              for (int e = h2 * 32; e < h2 * 32 + 32; e += 4) {
+                bwd_exp4(&sv[e], e, sc2, nl4[e >> 2], &pr[e]);
+                if (need_mask) {
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) pr[e + u] = (e + u >= q_min) ? pr[e + u] : 0.f;
+                }
+                pk[e / 2] = Pack2<T>::pack(pr[e], pr[e + 1]);
+                pk[e / 2 + 1] = Pack2<T>::pack(pr[e + 2], pr[e + 3]);
               }
-              pk[e / 2] = Pack2<T>::pack(pr[e], pr[e + 1]);
-              pk[e / 2 + 1] = Pack2<T>::pack(pr[e + 2], pr[e + 3]);
-            }
-            // the lower warps overwrite columns they have read themselves; the upper warps' P^T lands on
-            // columns [32,64), which the lower warps have read once half_read completes
-            if (half == 1) {
-              if (!mbar_wait_warp(&s.half_read[0], cnt & 1u, ctx, kBwdCons)) {
-                ok = false;
-                break;
+              // the lower warps overwrite columns they have read themselves; the upper warps' P^T lands on
+              // columns [32,64), which the lower warps have read once half_read completes
+              if (half == 1 && h2 == 0) {
+                if (!mbar_wait_warp(&s.half_read[0], cnt & 1u, ctx, kBwdCons)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
               }
-              tc_fence_after();
+              // 32 queries at a time, so that the matching part of dV += P^T dO starts behind the other 32
+              tmem_st16(tmem + lane_off + col_out + h2 * 16, pk + h2 * 16);
+              tmem_wait_st();
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&s.p_ready[h2]);
             }
-            tmem_st32(tmem + lane_off + col_out, pk);
+            if (!ok) break;
           }
-          tmem_wait_st();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&s.p_ready);
           // ---- phase B: dP -> dS = P o (dP - delta), 16-bit over dP^T for dK += dS^T Q ----
           if (!mbar_wait_warp(&s.dp_full, cnt & 1u, ctx, kBwdCons)) {
             ok = false;
@@ -575,14 +617,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
   const bool run = (s.abort_flag == 0);
   const int past = p.Skv - p.Sq;
 
-  auto item_of = [&](int g, int& b, int& hq, int& q0, int& nk) {
-    // heaviest query tiles (highest index under a causal mask) first
-    const int qb = p.nqb - 1 - (g % p.nqb);
-    const int bh = g / p.nqb;
+  // Work list: entry u >> 1 is a pair of query tiles (nqb-1-pair, pair) of one (batch, head), u & 1 selects
+  // the tile; under a causal mask the two together see about the same number of key tiles for every pair.
+  auto item_of = [&](int u, int& b, int& hq, int& q0, int& nk) -> bool {
+    const int g = u >> 1;
+    const int pair = g % p.npairs;
+    const int bh = g / p.npairs;
+    const int qb = (u & 1) ? pair : p.nqb - 1 - pair;
+    if ((u & 1) && qb == p.nqb - 1 - pair) return false;  // middle tile of an odd count
     b = bh / p.Hq;
     hq = bh - b * p.Hq;
     q0 = qb * 128;
     nk = p.causal ? min(p.nkb, (min(q0 + 127, p.Sq - 1) + past) / 128 + 1) : p.nkb;
+    return true;
   };
 
   if (warp == 8) {
@@ -590,9 +637,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
       // ---------------- TMA producer ----------------
       uint32_t cnt = 0, f_phase = 1;
       bool ok = true;
-      for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x) {
+      for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1)) {
         int b, hq, q0, nk;
-        item_of(g, b, hq, q0, nk);
+        if (!item_of(u, b, hq, q0, nk)) continue;
         const int hkv = hq / p.group;
         if (!mbar_wait(&s.fixed_empty, f_phase, ctx, kBwdTma)) break;
         f_phase ^= 1;
@@ -649,9 +696,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
         __syncwarp();
         return true;
       };
-      for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x, ++items) {
+      for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1), ++items) {
         int b, hq, q0, nk;
-        item_of(g, b, hq, q0, nk);
+        if (!item_of(u, b, hq, q0, nk)) {
+          --items;  // not an item: keep the count of real items
+          continue;
+        }
         if (!mbar_wait_warp(&s.fixed_full, f_phase, ctx, kBwdMma)) break;
         f_phase ^= 1;
         if (!issue_s(cnt) || !issue_dp(cnt)) break;
@@ -718,9 +768,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
     uint32_t cnt = 0, items = 0;
     bool ok = true;
     BWD_PROF_DECL
-    for (int g = blockIdx.x; ok && g < p.total_items; g += gridDim.x, ++items) {
+    for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1), ++items) {
       int b, hq, q0, nk;
-      item_of(g, b, hq, q0, nk);
+      if (!item_of(u, b, hq, q0, nk)) {
+        --items;  // not an item: keep the count of real items
+        continue;
+      }
       const int q = q0 + row_in_tile;
       const bool live = q < p.Sq;
       const long long stat = (static_cast<long long>(b) * p.Hq + hq) * p.Sq + q;
@@ -1007,8 +1060,9 @@ extern "C" int hb_fa_bwd_dkdv(const hb_fa_bwd_args* a) {
   BwdParams p;
   rc = bwd_fill(a, p, st);
   if (rc != HB_OK) return rc;
-  const long long total = (long long)a->B * a->Hkv * p.nkb;
-  if (total > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_bwd_dkdv: problem too large");
+  p.npairs = (p.nkb + 1) / 2;
+  const long long total = (long long)a->B * a->Hkv * p.npairs;
+  if (total > 0x3fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_bwd_dkdv: problem too large");
   p.total_items = (int)total;
   int grid = (int)std::min<long long>(total, st->sm_count);
 #ifdef HB_DEBUG_GRID_ENV  // measurement builds only: fewer CTAs than SMs
@@ -1040,8 +1094,9 @@ extern "C" int hb_fa_bwd_dq(const hb_fa_bwd_args* a) {
   BwdParams p;
   rc = bwd_fill(a, p, st);
   if (rc != HB_OK) return rc;
-  const long long total = (long long)a->B * a->Hq * p.nqb;
-  if (total > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_bwd_dq: problem too large");
+  p.npairs = (p.nqb + 1) / 2;
+  const long long total = (long long)a->B * a->Hq * p.npairs;
+  if (total > 0x3fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_bwd_dq: problem too large");
   p.total_items = (int)total;
   int grid = (int)std::min<long long>(total, st->sm_count);
 #ifdef HB_DEBUG_GRID_ENV  // measurement builds only: fewer CTAs than SMs
