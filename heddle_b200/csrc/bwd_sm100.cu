@@ -887,24 +887,25 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
 // (16 bytes each); a warp covers 4 * 256 / D rows with all eight 16-byte loads of a lane in flight at once.
 // ------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(256) fa_bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
+__global__ void __launch_bounds__(256, 4) fa_bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
                                                                  float* __restrict__ delta, int B, int H, int S,
                                                                  long long o_sb, long long o_sh, long long o_ss,
                                                                  long long g_sb, long long g_sh, long long g_ss) {
   constexpr int kLanesPerRow = D / 8, kRowsPerLoad = 32 / kLanesPerRow, kRowsPerWarp = 4 * kRowsPerLoad;
   const int lane = threadIdx.x & 31, sub = lane / kLanesPerRow, lr = lane % kLanesPerRow;
-  const long long total = static_cast<long long>(B) * H * S;
-  const long long row0 = (blockIdx.x * 8ll + (threadIdx.x >> 5)) * kRowsPerWarp;
+  // the host checks that B * H * S fits 31 bits: 32-bit divisions (the 64-bit ones are emulated and were
+  // a visible part of this short kernel)
+  const uint32_t total = static_cast<uint32_t>(B) * static_cast<uint32_t>(H) * static_cast<uint32_t>(S);
+  const uint32_t row0 = (blockIdx.x * 8u + (threadIdx.x >> 5)) * kRowsPerWarp;
   uint4 a[4], g[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const long long row = row0 + i * kRowsPerLoad + sub;
+    const uint32_t row = row0 + i * kRowsPerLoad + sub;
     a[i] = make_uint4(0u, 0u, 0u, 0u);
     g[i] = a[i];
     if (row < total) {
-      const int sq = static_cast<int>(row % S);
-      const long long bh = row / S;
-      const int h = static_cast<int>(bh % H), b = static_cast<int>(bh / H);
+      const uint32_t bh = row / static_cast<uint32_t>(S), sq = row - bh * static_cast<uint32_t>(S);
+      const uint32_t b = bh / static_cast<uint32_t>(H), h = bh - b * static_cast<uint32_t>(H);
       a[i] = *reinterpret_cast<const uint4*>(o + b * o_sb + h * o_sh + sq * o_ss + lr * 8);
       g[i] = *reinterpret_cast<const uint4*>(d_o + b * g_sb + h * g_sh + sq * g_ss + lr * 8);
     }
@@ -918,7 +919,7 @@ __global__ void __launch_bounds__(256) fa_bwd_preprocess_kernel(const T* __restr
     for (int e = 0; e < 8; ++e) acc = fmaf(static_cast<float>(ap[e]), static_cast<float>(gp[e]), acc);
 #pragma unroll
     for (int off = kLanesPerRow / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    const long long row = row0 + i * kRowsPerLoad + sub;
+    const uint32_t row = row0 + i * kRowsPerLoad + sub;
     if (lr == 0 && row < total) delta[row] = acc;
   }
 }
@@ -1024,6 +1025,7 @@ extern "C" int hb_fa_bwd_preprocess(const hb_fa_bwd_args* a) {
   if (a->B == 0 || a->Sq == 0) return HB_OK;
   if (a->o == nullptr || a->d_o == nullptr || a->delta == nullptr)
     return set_error(HB_ERR_BAD_ARG, "hb_fa_bwd_preprocess: o, d_o and delta must be non-NULL");
+  if ((long long)a->B * a->Hq * a->Sq > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_bwd_preprocess: problem too large");
   if ((reinterpret_cast<uintptr_t>(a->o) & 15) || (reinterpret_cast<uintptr_t>(a->d_o) & 15) || (a->o_stride_s & 7) ||
       (a->o_stride_h & 7) || (a->o_stride_b & 7) || (a->do_stride_s & 7) || (a->do_stride_h & 7) || (a->do_stride_b & 7))
     return set_error(HB_ERR_ALIGN, "hb_fa_bwd_preprocess: o and d_o need 16-byte aligned rows");
