@@ -343,6 +343,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
         if (leader) {
           bwd_mma_kk<T, D>(tmem + 128, s.fixed[1], s.ring_b[cnt & 1u]);  // dP^T = V dO^T
           umma_commit(&s.dp_full);
+          if (n_steps == 1) umma_commit(&s.fixed_empty);  // K and V are not read again
         }
         __syncwarp();
         BWD_PROF(0)
@@ -405,15 +406,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
             if (more) {
               bwd_mma_kk<T, D>(tmem + 128, s.fixed[1], s.ring_b[nx]);  // dP^T of the next step, over dS^T
               umma_commit(&s.dp_full);
+              // the item's last products with K and V are out: the next item's tiles load behind the last step
+              if (n + 2 == n_steps) umma_commit(&s.fixed_empty);
             }
           }
           __syncwarp();
           BWD_PROF(6)
         }
-        if (ok && leader) {
-          umma_commit(&s.acc_full);
-          umma_commit(&s.fixed_empty);
-        }
+        if (ok && leader) umma_commit(&s.acc_full);
         __syncwarp();
       }
       __syncwarp();
@@ -706,6 +706,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
         f_phase ^= 1;
         if (!issue_s(cnt) || !issue_dp(cnt)) break;
         if (nk > 1 && !issue_s(cnt + 1)) break;
+        if (nk == 1 && leader) umma_commit(&s.fixed_empty);  // Q and dO are not read again
+        __syncwarp();
         BWD_PROF(0)
         for (int n = 0; n < nk; ++n, ++cnt) {
           // the V tile of the next dP was requested a step ago: waited for before the consumers' result,
@@ -729,6 +731,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
               bwd_mma_kk<T, D>(tmem + 256, s.fixed[1], s.ring_b[(cnt + 1) & 1u]);
               umma_commit(&s.dp_full);
               umma_commit(&s.b_empty[(cnt + 1) & 1u]);
+              // the item's last products with Q and dO are out: the next item's tiles load behind the last step
+              if (n + 2 == nk) umma_commit(&s.fixed_empty);
             }
             bwd_mma_ts<T, D>(tmem + 384, tmem + (cnt & 1u) * 128u, s.ring_a[cnt % 3u], n > 0 ? 1u : 0u);  // dQ += dS K
             umma_commit(&s.a_empty[cnt % 3u]);
@@ -743,10 +747,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
           }
           BWD_PROF(4)
         }
-        if (ok && leader) {
-          umma_commit(&s.acc_full);
-          umma_commit(&s.fixed_empty);
-        }
+        if (ok && leader) umma_commit(&s.acc_full);
         __syncwarp();
       }
       __syncwarp();
