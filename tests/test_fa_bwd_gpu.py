@@ -180,3 +180,34 @@ def test_training_step_through_the_compiled_backend(ops):
         assert p_got.grad is not None, name
         err = (p_got.grad.float().cpu() - p_ref.grad).abs().max().item()
         assert err <= 3e-2 * max(p_ref.grad.abs().max().item(), 1e-3), (name, err, p_ref.grad.abs().max().item())
+
+
+def test_backward_full_length_properties(ops):
+    """Headline sequence length (S = 4096, D = 128, causal): a size-independent identity over all heads and
+    oracle parity on one head.  With dO = 1 every column of dV[b,h,k,:] is sum_q P[q,k], which is exactly the
+    H2O score that hb_h2o_score computes from the same LSE with another kernel."""
+    B, H, S, D = 2, 4, 4096, 128
+    q, k, v = O.make_qkv(B, H, H, S, S, D, seed=41, dtype=torch.bfloat16)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    out, lse = ops.fa_fwd(qc, kc, vc, causal=True, return_lse=True)
+    ones = torch.ones_like(qc)
+    _, _, dv1 = ops.fa_bwd(qc, kc, vc, out, ones, lse, causal=True)
+    score = ops.h2o_score(qc, kc, lse, causal=True)
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    ref = score.unsqueeze(-1).expand(-1, -1, -1, D)
+    # P is rounded to bf16 before the product (relative 2^-9 per term), the sum runs over up to 4096 terms
+    assert (dv1.float() - ref).abs().max().item() <= 1e-2 * max(1.0, score.max().item())
+    # columns of dV are identical for dO = 1
+    assert (dv1.float() - dv1.float()[..., :1]).abs().max().item() <= 2e-2 * max(1.0, score.max().item())
+    # one head against the oracle
+    d_o = _grad_out(B, H, S, D, 42, torch.bfloat16)
+    dq, dk, dv = ops.fa_bwd(qc, kc, vc, out, d_o.cuda(), lse, causal=True)
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    b, h = 1, 2
+    rq, rk, rv, _ = O.attention_backward(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1],
+                                         d_o[b:b + 1, h:h + 1], causal=True)
+    for name, got, ref1 in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        err = (got[b:b + 1, h:h + 1].cpu().float() - ref1).abs().max().item()
+        assert err <= _tol(torch.bfloat16, ref1), f"{name}: {err} (reference max {ref1.abs().max().item()})"
