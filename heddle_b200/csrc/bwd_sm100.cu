@@ -11,9 +11,9 @@
 // there.  The dK/dV kernel issues the products transposed (S^T = K Q^T, dP^T = V dO^T), so that a
 // key is a TMEM lane: P^T and dS^T are then exactly the A operands (from TMEM) of dV += P^T dO
 // and dK += dS^T Q, and each thread owns one key row.  The dQ kernel keeps queries on the lanes.
-// One CTA (320 threads): warps 0-7 turn scores into P / dS (a row is shared by two threads, warp w
-// takes columns [0,64) and warp w+4 columns [64,128) of the same 32 TMEM lanes; P stays in fp32
-// registers between the two phases), warp 8 is the TMA producer, warp 9 issues the MMAs.
+// One CTA (320 threads): warps 0-7 turn scores into P / dS (P stays in fp32 registers between the two
+// phases; in the dK/dV kernel a row is shared by two threads, warp w takes columns [0,64) and warp w+4
+// columns [64,128) of the same 32 TMEM lanes), warp 8 is the TMA producer, warp 9 issues the MMAs.
 //
 // Schedules (n = step, one 128 x 128 tile of scores; A = scores -> P, B = dP -> dS):
 //   dK/dV  tensor pipe:  S(0) dP(0) | dV(n) S(n+1) | dK(n) dP(n+1) | ...
@@ -22,7 +22,9 @@
 //          pipe; phase B(n) and the MMAs dK(n), dP(n+1) hide behind the chain A(n) -> dV(n) -> S(n+1).
 //   dQ     tensor pipe:  S(0) dP(0) S(1) | dP(n+1) dQ(n) S(n+2) | ...
 //          S is double-buffered (S0, S1, dP, dQ = 512 columns) and dS(n) is written over S(n), so the
-//          dP region is free as soon as phase B(n) has read it and phase A(n+1) hides behind dP(n+1).
+//          dP region is free as soon as phase B(n) has read it.  Here a thread owns a whole query row and
+//          the two groups of four consumer warps take alternate steps (group g = score buffer g): phase
+//          A(n+1) of one group runs beside phase B(n) of the other.
 // head_dim 128 or 64, bf16 / fp16.
 #include "host_common.h"
 #include "ptx_sm100.cuh"
@@ -33,7 +35,8 @@
 
 namespace hb {
 
-constexpr int kBwdThreads = 320;
+constexpr int kBwdThreads = 320;    // dK/dV kernel
+constexpr int kBwdDqThreads = 384;  // dQ kernel: a third (partly idle) warpgroup, so that registers can be re-split
 __host__ __device__ constexpr uint32_t bwd_tile_bytes(int d) { return 128u * static_cast<uint32_t>(d) * 2u; }  // one 128-row tile of a 16-bit tensor
 enum BwdRole : uint32_t { kBwdTma = 0x41, kBwdMma = 0x42, kBwdCons = 0x43, kBwdDrain = 0x44 };
 // Share of the exponentials evaluated on the FMA pipe instead of the MUFU: 0 none, 1 a quarter, 2 half.
@@ -204,7 +207,7 @@ __device__ __forceinline__ void bwd_exp4(const uint32_t* sv, int e, uint64_t sc2
 }
 
 template <typename Smem>
-__device__ __forceinline__ void bwd_init(Smem& s, const AbortCtx& ctx, const void* smem_raw) {
+__device__ __forceinline__ void bwd_init(Smem& s, const AbortCtx& ctx, const void* smem_raw, uint32_t ds_arrivals) {
   s.abort_flag = 0;
   mbar_init(&s.fixed_full, 1);
   mbar_init(&s.fixed_empty, 1);
@@ -221,7 +224,7 @@ __device__ __forceinline__ void bwd_init(Smem& s, const AbortCtx& ctx, const voi
   mbar_init(&s.dp_full, 1);
   mbar_init(&s.p_ready[0], 8);
   mbar_init(&s.p_ready[1], 8);
-  mbar_init(&s.ds_ready, 8);
+  mbar_init(&s.ds_ready, ds_arrivals);
   mbar_init(&s.half_read[0], 4);
   mbar_init(&s.half_read[1], 4);
   mbar_init(&s.acc_full, 1);
@@ -244,7 +247,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{&s.abort_flag, p.status};
   if (threadIdx.x == 0) {
-    bwd_init(s, ctx, smem_raw);
+    bwd_init(s, ctx, smem_raw, 8);
     prefetch_tensormap(&p.tm_q);
     prefetch_tensormap(&p.tm_k);
     prefetch_tensormap(&p.tm_v);
@@ -592,7 +595,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
 // TMEM: S buffers [0,128) [128,256), dP [256,384), dQ [384,512).
 // ------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kBwdDqThreads, 1) fa_bwd_dq_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   using Smem = BwdSmemQ<D>;
   constexpr uint32_t kBwdTileBytes = bwd_tile_bytes(D);
@@ -600,7 +603,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{&s.abort_flag, p.status};
   if (threadIdx.x == 0) {
-    bwd_init(s, ctx, smem_raw);
+    bwd_init(s, ctx, smem_raw, 4);
     prefetch_tensormap(&p.tm_q);
     prefetch_tensormap(&p.tm_k);
     prefetch_tensormap(&p.tm_v);
@@ -632,6 +635,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
     return true;
   };
 
+  // Registers: the consumers keep a whole row of P (128 fp32) between the phases; warps 8-11 give theirs up
+  // (setmaxnreg is per warpgroup: warps 10 and 11 exist only for that).  Per scheduler 2 x 216 + 72 <= 512.
+  if (warp >= 8) reg_dec<72>();
   if (warp == 8) {
     if (run && lane == 0) {
       // ---------------- TMA producer ----------------
@@ -758,13 +764,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
       }
     }
     __syncwarp();
-  } else if (run) {
-    // ---------------- consumers: one query per pair of threads ----------------
-    const int slab = warp & 3, half = warp >> 2;
+  } else if (warp < 8) {
+   reg_inc<216>();
+   if (run) {
+    // ---------------- consumers: one query per thread, the two groups of four warps take alternate steps ----------------
+    // Group g owns the steps whose global index is g modulo 2, i.e. score buffer g.  While one group turns dP of
+    // step n into dS (the link of the chain dS(n) -> dP(n+1) -> dS(n+1)), the other is already past the
+    // exponentials of step n+1 and only waits for its dP.
+    const int slab = warp & 3, grp = warp >> 2;
     const int row_in_tile = slab * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(slab * 32) << 16;
-    const uint32_t col_in = static_cast<uint32_t>(half * 64);
-    const uint32_t col_out = static_cast<uint32_t>(half * 32);
+    const uint32_t sbuf = tmem + lane_off + static_cast<uint32_t>(grp) * 128u;
     const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
     uint32_t cnt = 0, items = 0;
     bool ok = true;
@@ -782,71 +792,53 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
       const float dlt = live ? __ldg(p.delta + stat) : 0.f;
       const float4 l4 = make_float4(nlse2, nlse2, nlse2, nlse2);
       for (int kt = 0; kt < nk; ++kt, ++cnt) {
-        const uint32_t sbuf = tmem + lane_off + (cnt & 1u) * 128u;
+        if ((cnt & 1u) != static_cast<uint32_t>(grp)) continue;
         // ---- phase A: scores -> P in registers ----
-        if (!mbar_wait_warp(&s.s_full[cnt & 1u], (cnt >> 1) & 1u, ctx, kBwdCons)) {
+        if (!mbar_wait_warp(&s.s_full[grp], (cnt >> 1) & 1u, ctx, kBwdCons)) {
           ok = false;
           break;
         }
         tc_fence_after();
         BWD_PROF(0)
-        float pr[64];
-        {
-          uint32_t sv[64];
-          tmem_ld32(sbuf + col_in, sv);
-          tmem_ld32(sbuf + col_in + 32, sv + 32);
-          tmem_wait_ld();
-          BWD_PROF(1)
-          if (half == 0) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s.half_read[cnt & 1u]);
-          }
-          // keys this query sees among this thread's columns: key <= q + past (causal) and key < Skv
-          int lim = p.Skv - 1 - kt * 128;
-          if (p.causal) lim = min(lim, q + past - kt * 128);
-          lim -= half * 64;
-          const bool need_mask = (kt * 128 + 127 >= p.Skv) || (p.causal && kt * 128 + 127 > q0 + past);
+        // keys this query sees in the tile: key <= q + past (causal) and key < Skv
+        int lim = p.Skv - 1 - kt * 128;
+        if (p.causal) lim = min(lim, q + past - kt * 128);
+        const bool need_mask = (kt * 128 + 127 >= p.Skv) || (p.causal && kt * 128 + 127 > q0 + past);
+        float pr[128];
 #pragma unroll
-          for (int e = 0; e < 64; e += 4) {
-            bwd_exp4(&sv[e], e, sc2, l4, &pr[e]);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sv[32];
+          tmem_ld32(sbuf + c * 32, sv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            bwd_exp4(&sv[e], e, sc2, l4, &pr[c * 32 + e]);
             if (need_mask) {
 #pragma unroll
-              for (int u = 0; u < 4; ++u) pr[e + u] = (e + u <= lim) ? pr[e + u] : 0.f;
+              for (int w = 0; w < 4; ++w) pr[c * 32 + e + w] = (c * 32 + e + w <= lim) ? pr[c * 32 + e + w] : 0.f;
             }
           }
         }
         BWD_PROF(2)
-        // ---- phase B: dP -> dS, 16-bit over the score buffer of the step ----
+        // ---- phase B: dP -> dS, 16-bit over the score buffer of the step (all of it is in registers by now) ----
         if (!mbar_wait_warp(&s.dp_full, cnt & 1u, ctx, kBwdCons)) {
           ok = false;
           break;
         }
         tc_fence_after();
         BWD_PROF(3)
-        {
-          uint32_t dv[64], dk[32];
-          tmem_ld32(tmem + lane_off + 256 + col_in, dv);
-          tmem_ld32(tmem + lane_off + 256 + col_in + 32, dv + 32);
-          tmem_wait_ld();
-          BWD_PROF(4)
 #pragma unroll
-          for (int e = 0; e < 64; e += 2) {
-            const float x0 = pr[e] * (__uint_as_float(dv[e]) - dlt);
-            const float x1 = pr[e + 1] * (__uint_as_float(dv[e + 1]) - dlt);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t dv[32], dk[16];
+          tmem_ld32(tmem + lane_off + 256 + c * 32, dv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float x0 = pr[c * 32 + e] * (__uint_as_float(dv[e]) - dlt);
+            const float x1 = pr[c * 32 + e + 1] * (__uint_as_float(dv[e + 1]) - dlt);
             dk[e / 2] = Pack2<T>::pack(x0, x1);
           }
-          BWD_PROF(5)
-          // the upper warps' dS lands on score columns [32,64), which the lower warps read in phase A
-          if (half == 1) {
-            if (!mbar_wait_warp(&s.half_read[cnt & 1u], (cnt >> 1) & 1u, ctx, kBwdCons)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-          }
-          BWD_PROF(6)
-          tmem_st32(sbuf + col_out, dk);
+          tmem_st16(sbuf + c * 16, dk);
         }
         tmem_wait_st();
         tc_fence_before();
@@ -857,7 +849,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
       if (!ok) break;
       if (!mbar_wait_warp(&s.acc_full, items & 1u, ctx, kBwdCons)) break;
       tc_fence_after();
-      const uint32_t col_acc = static_cast<uint32_t>(half * (D / 2));
+      const uint32_t col_acc = static_cast<uint32_t>(grp * (D / 2));
       T* dq_row = static_cast<T*>(p.dq) + stat * D + col_acc;
 #pragma unroll 1
       for (int c = 0; c < D / 64; ++c) {
@@ -873,6 +865,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dq_kernel(const __grid_
       BWD_PROF(0)
     }
     BWD_PROF_FLUSH
+   }
   }
 
   tc_fence_before();
@@ -981,7 +974,7 @@ static int bwd_fill(const hb_fa_bwd_args* a, BwdParams& p, const DeviceState* st
 }
 
 template <typename Smem>
-static int bwd_launch(void (*kernel)(const BwdParams), const BwdParams& p, int grid, const DeviceState* st,
+static int bwd_launch(void (*kernel)(const BwdParams), const BwdParams& p, int grid, int threads, const DeviceState* st,
                       cudaStream_t stream, bool* configured) {
   if ((int)sizeof(Smem) > st->smem_optin)
     return set_error(HB_ERR_UNSUPPORTED, "attention backward needs %d bytes of shared memory per CTA, the device offers %d",
@@ -990,19 +983,19 @@ static int bwd_launch(void (*kernel)(const BwdParams), const BwdParams& p, int g
     HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
     configured[st->device & 63] = true;
   }
-  kernel<<<grid, kBwdThreads, sizeof(Smem), stream>>>(p);
+  kernel<<<grid, threads, sizeof(Smem), stream>>>(p);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB_OK;
 }
 template <typename T, int D>
 static int launch_dkdv(const BwdParams& p, int grid, const DeviceState* st, cudaStream_t stream) {
   static bool configured[64] = {};
-  return bwd_launch<BwdSmemKv<D>>(fa_bwd_dkdv_kernel<T, D>, p, grid, st, stream, configured);
+  return bwd_launch<BwdSmemKv<D>>(fa_bwd_dkdv_kernel<T, D>, p, grid, kBwdThreads, st, stream, configured);
 }
 template <typename T, int D>
 static int launch_dq(const BwdParams& p, int grid, const DeviceState* st, cudaStream_t stream) {
   static bool configured[64] = {};
-  return bwd_launch<BwdSmemQ<D>>(fa_bwd_dq_kernel<T, D>, p, grid, st, stream, configured);
+  return bwd_launch<BwdSmemQ<D>>(fa_bwd_dq_kernel<T, D>, p, grid, kBwdDqThreads, st, stream, configured);
 }
 template <typename T, int D>
 static int launch_preprocess(const hb_fa_bwd_args* a, cudaStream_t stream) {
