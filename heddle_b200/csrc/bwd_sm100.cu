@@ -434,7 +434,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
     const uint32_t lane_off = static_cast<uint32_t>(slab * 32) << 16;
     const uint32_t col_in = static_cast<uint32_t>(half * 64);   // fp32 columns this thread reads
     const uint32_t col_out = static_cast<uint32_t>(half * 32);  // 16-bit columns it writes
-    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2);
+    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), one2 = pack_f32x2(1.0f, 1.0f);
     uint32_t cnt = 0, items = 0;
     bool ok = true;
     for (int u = 2 * blockIdx.x; ok && u < 2 * p.total_items; u += ((u & 1) ? 2 * (int)gridDim.x - 1 : 1), ++items) {
@@ -534,10 +534,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) fa_bwd_dkdv_kernel(const __gri
 #pragma unroll
             for (int e = 0; e < 64; e += 4) {
               const float4 d4 = dl4[e >> 2];
-              const float x0 = pr[e] * (__uint_as_float(dv[e]) - d4.x);
-              const float x1 = pr[e + 1] * (__uint_as_float(dv[e + 1]) - d4.y);
-              const float x2 = pr[e + 2] * (__uint_as_float(dv[e + 2]) - d4.z);
-              const float x3 = pr[e + 3] * (__uint_as_float(dv[e + 3]) - d4.w);
+              // two elements per instruction: (dP - delta) as dP * 1 + (-delta), then P * that
+              const uint64_t t01 = fma_f32x2(pack_f32x2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), one2, pack_f32x2(-d4.x, -d4.y));
+              const uint64_t t23 = fma_f32x2(pack_f32x2(__uint_as_float(dv[e + 2]), __uint_as_float(dv[e + 3])), one2, pack_f32x2(-d4.z, -d4.w));
+              float x0, x1, x2, x3;
+              unpack_f32x2(mul_f32x2(pack_f32x2(pr[e], pr[e + 1]), t01), x0, x1);
+              unpack_f32x2(mul_f32x2(pack_f32x2(pr[e + 2], pr[e + 3]), t23), x2, x3);
               dk[e / 2] = Pack2<T>::pack(x0, x1);
               dk[e / 2 + 1] = Pack2<T>::pack(x2, x3);
             }
@@ -791,6 +793,7 @@ __global__ void __launch_bounds__(kBwdDqThreads, 1) fa_bwd_dq_kernel(const __gri
       const float nlse2 = live ? -__ldg(p.lse + stat) * 1.4426950408889634f : -INFINITY;
       const float dlt = live ? __ldg(p.delta + stat) : 0.f;
       const float4 l4 = make_float4(nlse2, nlse2, nlse2, nlse2);
+      const uint64_t ndl2 = pack_f32x2(-dlt, -dlt);
       for (int kt = 0; kt < nk; ++kt, ++cnt) {
         if ((cnt & 1u) != static_cast<uint32_t>(grp)) continue;
         // ---- phase A: scores -> P in registers ----
@@ -834,8 +837,10 @@ __global__ void __launch_bounds__(kBwdDqThreads, 1) fa_bwd_dq_kernel(const __gri
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            const float x0 = pr[c * 32 + e] * (__uint_as_float(dv[e]) - dlt);
-            const float x1 = pr[c * 32 + e + 1] * (__uint_as_float(dv[e + 1]) - dlt);
+            // two elements per instruction: (dP - delta), then P * that
+            const uint64_t t2 = add_f32x2(pack_f32x2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), ndl2);
+            float x0, x1;
+            unpack_f32x2(mul_f32x2(pack_f32x2(pr[c * 32 + e], pr[c * 32 + e + 1]), t2), x0, x1);
             dk[e / 2] = Pack2<T>::pack(x0, x1);
           }
           tmem_st16(sbuf + c * 16, dk);
