@@ -27,7 +27,9 @@ os.environ["TILELANG_FRONTEND_EXECUTE_PARTITIONS"] = "0"
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
-sys.path.insert(0, os.environ.get("HEDDLE_REFERENCE", "/root/reference/Heddle"))
+if "HEDDLE_REFERENCE" not in os.environ:
+    raise SystemExit("set HEDDLE_REFERENCE to the directory of the reference checkout that holds the heddle package")
+sys.path.insert(0, os.environ["HEDDLE_REFERENCE"])
 
 import torch  # noqa: E402
 
