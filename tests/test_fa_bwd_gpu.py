@@ -211,3 +211,23 @@ def test_backward_full_length_properties(ops):
     for name, got, ref1 in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
         err = (got[b:b + 1, h:h + 1].cpu().float() - ref1).abs().max().item()
         assert err <= _tol(torch.bfloat16, ref1), f"{name}: {err} (reference max {ref1.abs().max().item()})"
+
+
+def test_bshd_strided_gqa_backward(ops):
+    """(B, S, H, D) views with grouped queries straight through ops.fa_bwd: strides are passed on, nothing is
+    copied, dK / dV come back as (B, S, Hkv, D) views."""
+    B, S, Hq, Hkv, D = 2, 300, 6, 2, 128
+    g = torch.Generator().manual_seed(51)
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, generator=g).to(torch.bfloat16).cuda()   # one packed projection output
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]              # non-contiguous views
+    d_o = torch.randn(B, S, Hq, D, generator=g).to(torch.bfloat16).cuda()
+    out, lse = ops.fa_fwd(q, k, v, causal=True, layout="bshd", return_lse=True)
+    dq, dk, dv = ops.fa_bwd(q, k, v, out, d_o, lse, causal=True, layout="bshd")
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+    t = lambda x: x.transpose(1, 2).float().cpu()
+    rq, rk, rv, _ = O.attention_backward(t(q), t(k), t(v), t(d_o), causal=True)
+    for name, got, ref in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        err = (t(got) - ref).abs().max().item()
+        assert err <= _tol(torch.bfloat16, ref), f"{name}: {err} (reference max {ref.abs().max().item()})"
