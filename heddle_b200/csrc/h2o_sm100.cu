@@ -7,7 +7,7 @@
 // transposed, S^T = K Q^T, so that a key is a TMEM lane: each thread owns one key, the sum
 // over queries is a plain per-thread accumulation and needs no cross-thread reduction.
 //
-// CTA (320 threads), one 128-key tile of one (batch, head) at a time:
+// CTA (384 threads), one 128-key tile of one (batch, head) at a time:
 //   warps 0-3   consumer group 0: even query tiles      exp2(s*scale*log2e - LSE*log2e), masks,
 //   warps 4-7   consumer group 1: odd query tiles       per-key running sum
 //   warp 8      TMA: the K tile (A operand) once per work item, a ring of Q tiles (B operand)
@@ -22,7 +22,7 @@
 
 namespace hb {
 
-constexpr int kH2oThreads = 320;
+constexpr int kH2oThreads = 384;  // warps 10, 11 only complete the third warpgroup for setmaxnreg
 constexpr int kH2oStages = 4;
 enum H2oRole : uint32_t { kH2oTma = 0x31, kH2oMma = 0x32, kH2oCons = 0x33, kH2oDrain = 0x34 };
 
@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
   constexpr uint32_t kTileBytes = Smem::kTileBytes;
   constexpr uint32_t kHalfBytes = 128 * 128;
 
+  // the consumers hold a 128-column tile in registers: they take the registers warps 8-11 do not need
+  if (warp >= 8) reg_dec<72>();
   if (warp == 8) {
     if (run && lane == 0) {
       // ---------------- TMA producer ----------------
@@ -191,7 +193,9 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
       }
     }
     __syncwarp();
-  } else if (warp < 8 && run) {
+  } else if (warp < 8) {
+   reg_inc<208>();
+   if (run) {
     // ---------------- consumers ----------------
     const int grp = warp >> 2;                    // 0 or 1
     const int key_in_tile = (warp & 3) * 32 + lane;
@@ -280,6 +284,7 @@ __global__ void __launch_bounds__(kH2oThreads, 1) h2o_score_kernel(const __grid_
       // the two groups add their halves into the zero-initialised output (two commutative adds)
       if (key < p.Skv) atomicAdd(p.score + (static_cast<long long>(it.b) * p.Hq + it.hq) * p.Skv + key, sum);
     }
+   }
   }
 
   tc_fence_before();
