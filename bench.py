@@ -429,6 +429,31 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.kernel_only and not args.no_reference_gpu:
         ref_gpu = reference_gpu_kernel(B, H, S, D, causal)
 
+    # ---- attention backward on the same shape (informative; not part of the headline metric) ----
+    backward = None
+    if rank == 0 and world == 1 and not args.kernel_only:
+        try:
+            _, lse = ops.fa_fwd(q, k, v, causal=causal, out=out, return_lse=True)
+            d_o = torch.randn_like(q)
+            for _ in range(3):
+                ops.fa_bwd(q, k, v, out, d_o, lse, causal=causal)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            ev0.record()
+            for _ in range(20):
+                ops.fa_bwd(q, k, v, out, d_o, lse, causal=causal)
+            ev1.record()
+            torch.cuda.synchronize()
+            bwd_ms = ev0.elapsed_time(ev1) / 20
+            prod = 2.0 * B * H * S * S * D * (0.5 if causal else 1.0)  # flops of one S x S x D product
+            backward = {"ms": bwd_ms, "value": 5.0 * prod / (bwd_ms * 1e-3) / 1e12, "unit": UNIT,
+                        "executed_tflops": 7.0 * prod / (bwd_ms * 1e-3) / 1e12,
+                        "what": "hb_fa_bwd_preprocess + hb_fa_bwd_dkdv + hb_fa_bwd_dq, 20 backward passes; value counts the "
+                                "usual five products, executed_tflops the seven the two kernels issue",
+                        "device_status_word": ops.status_word()}
+        except Exception as exc:  # informative only
+            backward = {"error": str(exc)[:120]}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -439,6 +464,7 @@ def run_ours(args):
                        "l2": "inputs+outputs (268 MB per step) exceed the 126 MB L2; no explicit flush"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * world,
             "clocks": clocks.summary(), "sustained": sustained, "device_status_word": status, "reference_gpu_kernel": ref_gpu,
+            "backward": backward,
             "pct_of_nominal_dense_bf16_peak_2250": 100.0 * value / world / 2250.0,
         }
         print(json.dumps(line), flush=True)
