@@ -81,3 +81,35 @@ def test_two_ranks_tile_the_problem_or_report_failure(tmp_path, fail_rank):
         assert res == [["0", "1"], ["0", "1"]]
     else:
         assert res == [["1", "0"], ["1", "0"]]   # every rank learnt of the failure, none hung
+
+
+def _bwd_worker(rank, world, port, out_dir):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import attention_oracle as O
+        B, Hq, Hkv, S, D = 2, 4, 2, 64, 32
+        q, k, v = O.make_qkv(B, Hq, Hkv, S, S, D, seed=3)
+        d_o = torch.randn(B, Hq, S, D, generator=torch.Generator().manual_seed(4))
+        g = Hq // Hkv
+        dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+        # the backward shards exactly like the forward: a (batch, kv head) run owns its query heads' dQ and its own
+        # dK, dV (the sum over the group's query heads stays inside the run), so no rank needs another rank's data
+        for b, h0, h1 in sharding.shard_batch_kvheads(B, Hkv, world, rank):
+            rq, rk, rv, _ = O.attention_backward(q[b:b + 1, h0 * g:h1 * g], k[b:b + 1, h0:h1], v[b:b + 1, h0:h1],
+                                                 d_o[b:b + 1, h0 * g:h1 * g], causal=True)
+            dq[b, h0 * g:h1 * g], dk[b, h0:h1], dv[b, h0:h1] = rq[0], rk[0], rv[0]
+        for t in (dq, dk, dv):
+            dist.all_reduce(t)   # only to check the result; the data path itself has no collective
+        fq, fk, fv, _ = O.attention_backward(q, k, v, d_o, causal=True)
+        ok = all(torch.allclose(a, b_, atol=2e-5) for a, b_ in ((dq, fq), (dk, fk), (dv, fv)))
+        Path(out_dir, f"bwd_rank{rank}.txt").write_text(str(int(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_tile_the_backward(tmp_path):
+    port = 29500 + (os.getpid() % 2000) + 13
+    mp.spawn(_bwd_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert [Path(tmp_path, f"bwd_rank{r}.txt").read_text() for r in range(2)] == ["1", "1"]
