@@ -103,7 +103,7 @@ class PrepareArgs(C.Structure):
 
 # every symbol include/heddle_b200.h declares
 EXPORTS = (
-    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_status_word",
+    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_status_word_noalloc", "hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_status_word",
     "hb_version",
     "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma", "hb_debug_wait_timeout",
 )
@@ -143,6 +143,8 @@ def load() -> C.CDLL:
     lib.hb_row_softmax.restype = C.c_int
     lib.hb_status_word.argtypes = [C.POINTER(C.c_uint32)]
     lib.hb_status_word.restype = C.c_int
+    lib.hb_status_word_noalloc.argtypes = [C.POINTER(C.c_uint32), C.c_void_p]
+    lib.hb_status_word_noalloc.restype = C.c_int
     lib.hb_version.argtypes = []
     lib.hb_version.restype = C.c_int
     lib.hb_query.argtypes = [C.c_int]

@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <mutex>
 
 namespace hb {
 
@@ -16,6 +17,8 @@ template <typename T, int D>
 struct FaConfig {
   static constexpr int kStages = (D == 128 && FaTraits<T>::kElemBytes == 2) ? 5 : 8;
 };
+
+static std::mutex g_fa_mutex;  // guards the per-device set-up tables below
 
 template <typename T, int D>
 static int launch_fa(const FaParams& p, int grid, int smem_optin, cudaStream_t stream) {
@@ -28,57 +31,87 @@ static int launch_fa(const FaParams& p, int grid, int smem_optin, cudaStream_t s
   static bool configured[64] = {};
   int dev = 0;
   HB_CUDA_CHECK(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
-    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-    configured[dev & 63] = true;
+  {
+    std::lock_guard<std::mutex> lock(g_fa_mutex);
+    if (!configured[dev & 63]) {
+      HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+      configured[dev & 63] = true;
+    }
   }
   kernel<<<grid, kFaThreads, sizeof(Smem), stream>>>(p);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB_OK;
 }
 
+static int dispatch_fa(const hb_fa_args* a, const FaParams& p, int grid, int smem_optin) {
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (a->dtype == HB_FP8_E4M3) return launch_fa<__nv_fp8_e4m3, 128>(p, grid, smem_optin, stream);
+  if (a->dtype == HB_BF16) {
+    return a->D == 128 ? launch_fa<__nv_bfloat16, 128>(p, grid, smem_optin, stream)
+                       : launch_fa<__nv_bfloat16, 64>(p, grid, smem_optin, stream);
+  }
+  return a->D == 128 ? launch_fa<__half, 128>(p, grid, smem_optin, stream)
+                     : launch_fa<__half, 64>(p, grid, smem_optin, stream);
+}
+
 #ifdef HB_FA_TRACE
 static unsigned long long* g_trace_ptr = nullptr;
 #endif
 
-static int fa_fwd_impl(const hb_fa_args* a) {
-  if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: args is NULL");
+// Argument checks shared by hb_fa_fwd and hb_fa_fwd_noalloc (`who` names the entry point in
+// messages).  *empty is set when there is nothing to compute.
+static int fa_validate(const hb_fa_args* a, const char* who, bool allow_fp8, bool* empty) {
+  *empty = false;
+  if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "%s: args is NULL", who);
   if (a->B < 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq < 0 || a->Skv < 0 || a->D <= 0)
-    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: negative or zero extent (B=%d Hq=%d Hkv=%d Sq=%d Skv=%d D=%d)", a->B,
+    return set_error(HB_ERR_BAD_ARG, "%s: negative or zero extent (B=%d Hq=%d Hkv=%d Sq=%d Skv=%d D=%d)", who, a->B,
                      a->Hq, a->Hkv, a->Sq, a->Skv, a->D);
   if (a->Hq % a->Hkv != 0)
-    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
+    return set_error(HB_ERR_BAD_ARG, "%s: Hq=%d is not a multiple of Hkv=%d", who, a->Hq, a->Hkv);
   if (a->dtype != HB_BF16 && a->dtype != HB_FP16 && a->dtype != HB_FP8_E4M3)
-    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: unknown dtype %d", a->dtype);
+    return set_error(HB_ERR_UNSUPPORTED, "%s: unknown dtype %d", who, a->dtype);
+  if (a->dtype == HB_FP8_E4M3 && !allow_fp8)
+    return set_error(HB_ERR_UNSUPPORTED, "%s: dtype %d not supported (bf16, fp16)", who, a->dtype);
   if (a->D != 64 && a->D != 128)
-    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: head_dim %d not supported (64 or 128)", a->D);
+    return set_error(HB_ERR_UNSUPPORTED, "%s: head_dim %d not supported (64 or 128)", who, a->D);
   if (a->dtype == HB_FP8_E4M3 && a->D != 128)
-    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: FP8 needs head_dim 128 (got %d)", a->D);
-  if (a->B == 0 || a->Sq == 0) return HB_OK;  // nothing to compute
-  if (a->Skv == 0) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: Skv is 0 (softmax over an empty set)");
+    return set_error(HB_ERR_UNSUPPORTED, "%s: FP8 needs head_dim 128 (got %d)", who, a->D);
+  if (a->B == 0 || a->Sq == 0) {
+    *empty = true;
+    return HB_OK;
+  }
+  if (a->Skv == 0) return set_error(HB_ERR_BAD_ARG, "%s: Skv is 0 (softmax over an empty set)", who);
   if (a->causal && a->Skv < a->Sq)
-    return set_error(HB_ERR_UNSUPPORTED,
-                     "hb_fa_fwd: causal attention needs Skv >= Sq (the reference asserts past_len >= 0)");
+    return set_error(HB_ERR_UNSUPPORTED, "%s: causal attention needs Skv >= Sq (the reference asserts past_len >= 0)",
+                     who);
   if (a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr)
-    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd: q, k, v and o must be non-NULL");
-  const size_t es = dtype_size(a->dtype);
+    return set_error(HB_ERR_BAD_ARG, "%s: q, k, v and o must be non-NULL", who);
   const size_t eso = 2;  // O is 16-bit for every input dtype
   if ((reinterpret_cast<uintptr_t>(a->o) & 15u) != 0 || ((a->o_stride_s * eso) & 15u) != 0 ||
       ((a->o_stride_h * eso) & 15u) != 0 || ((a->o_stride_b * eso) & 15u) != 0)
-    return set_error(HB_ERR_ALIGN, "hb_fa_fwd: o and its strides must be 16-byte aligned");
+    return set_error(HB_ERR_ALIGN, "%s: o and its strides must be 16-byte aligned", who);
   if (a->lse != nullptr && (reinterpret_cast<uintptr_t>(a->lse) & 3u) != 0)
-    return set_error(HB_ERR_ALIGN, "hb_fa_fwd: lse must be 4-byte aligned");
+    return set_error(HB_ERR_ALIGN, "%s: lse must be 4-byte aligned", who);
+  // The work list is indexed with 32-bit integers; this is the largest problem one launch takes.
+  const int nqb = (a->Sq + 2 * kTileM - 1) / (2 * kTileM);
+  const long long total = (long long)a->B * a->Hq * ((nqb + 1) / 2);
+  if (total > 0x7fffffffLL)
+    return set_error(HB_ERR_UNSUPPORTED, "%s: problem too large (%lld query blocks, limit %d)", who, total, 0x7fffffff);
+  return HB_OK;
+}
 
-  DeviceState* st = nullptr;
-  int rc = get_device_state(&st);
-  if (rc != HB_OK) return rc;
-
-  FaParams p;
+// Kernel parameters of a validated call: tensor maps over the caller's q, k, v (by strides, so
+// BHSD, BSHD and packed views need no copy), the work-list geometry and the scales.  The tensor-map
+// encoder must be initialised (get_device_state / get_device_info_noalloc do that).
+static int fa_fill_params(const hb_fa_args* a, const char* who, uint32_t* status, FaParams* out) {
+  FaParams& p = *out;
   memset(&p, 0, sizeof(p));
+  const size_t es = dtype_size(a->dtype);
   const CUtensorMapDataType dt = a->dtype == HB_BF16   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                  : a->dtype == HB_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                        : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const uint32_t box[4] = {(uint32_t)(128 / es), (uint32_t)kTileM, 1, 1};  // 128 bytes of head_dim x 128 rows
+  int rc;
   {
     const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Sq, (uint64_t)a->Hq, (uint64_t)a->B};
     const uint64_t str[3] = {(uint64_t)a->q_stride_s * es, (uint64_t)a->q_stride_h * es, (uint64_t)a->q_stride_b * es};
@@ -99,7 +132,7 @@ static int fa_fwd_impl(const hb_fa_args* a) {
   }
   p.o = a->o;
   p.lse = a->lse;
-  p.status = st->status_word;
+  p.status = status;
 #ifdef HB_FA_TRACE
   p.trace = g_trace_ptr;
 #endif
@@ -115,9 +148,7 @@ static int fa_fwd_impl(const hb_fa_args* a) {
   p.causal = a->causal ? 1 : 0;
   p.nqb = (a->Sq + 2 * kTileM - 1) / (2 * kTileM);
   p.npairs = (p.nqb + 1) / 2;
-  const long long total = (long long)a->B * a->Hq * p.npairs;
-  if (total > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: problem too large (%lld blocks)", total);
-  p.total_pairs = (int)total;
+  p.total_pairs = (int)((long long)a->B * a->Hq * p.npairs);
   p.nkv = (a->Skv + kTileN - 1) / kTileN;
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->D);
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -128,23 +159,29 @@ static int fa_fwd_impl(const hb_fa_args* a) {
     const float qs = a->q_scale > 0.f ? a->q_scale : 1.0f, ks = a->k_scale > 0.f ? a->k_scale : 1.0f;
     const float vs = a->v_scale > 0.f ? a->v_scale : 1.0f, os = a->o_scale > 0.f ? a->o_scale : 1.0f;
     if (a->p_scale > 0.f && a->p_scale != 1.0f / FaTraits<__nv_fp8_e4m3>::kPScale)
-      return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd: p_scale is fixed at 1/%d in this build (pass 0)",
+      return set_error(HB_ERR_UNSUPPORTED, "%s: p_scale is fixed at 1/%d in this build (pass 0)", who,
                        (int)FaTraits<__nv_fp8_e4m3>::kPScale);
     p.scale_log2 *= qs * ks;
     p.out_scale = vs / (FaTraits<__nv_fp8_e4m3>::kPScale * os);
   }
+  return HB_OK;
+}
 
-  int grid = (int)std::min<long long>(total, st->sm_count);
+static int fa_fwd_impl(const hb_fa_args* a) {
+  bool empty = false;
+  int rc = fa_validate(a, "hb_fa_fwd", /*allow_fp8=*/true, &empty);
+  if (rc != HB_OK || empty) return rc;
+  DeviceState* st = nullptr;
+  rc = get_device_state(&st);
+  if (rc != HB_OK) return rc;
+  FaParams p;
+  rc = fa_fill_params(a, "hb_fa_fwd", st->status_word, &p);
+  if (rc != HB_OK) return rc;
+  int grid = std::min(p.total_pairs, st->sm_count);
 #ifdef HB_DEBUG_GRID_ENV  // measurement builds only: fewer CTAs than SMs, to see how the per-SM rate depends on the load on L2
   if (const char* e = getenv("HB_GRID")) grid = std::max(1, std::min(grid, atoi(e)));
 #endif
-  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  if (a->dtype == HB_FP8_E4M3) return launch_fa<__nv_fp8_e4m3, 128>(p, grid, st->smem_optin, stream);
-  if (a->dtype == HB_BF16) {
-    return a->D == 128 ? launch_fa<__nv_bfloat16, 128>(p, grid, st->smem_optin, stream)
-                       : launch_fa<__nv_bfloat16, 64>(p, grid, st->smem_optin, stream);
-  }
-  return a->D == 128 ? launch_fa<__half, 128>(p, grid, st->smem_optin, stream) : launch_fa<__half, 64>(p, grid, st->smem_optin, stream);
+  return dispatch_fa(a, p, grid, st->smem_optin);
 }
 
 // ------------------------------------------------------------------------------------
@@ -167,105 +204,63 @@ constexpr size_t kFaScratchNeeded = sizeof(uint32_t);
 // comes from cudaGetSymbolAddress, asked once per device with that device current.
 static void* g_fa_noalloc_ptr[64] = {};
 
-static int fa_fwd_noalloc_impl(const hb_fa_args* a) {
-  if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: args is NULL");
-  if (a->B < 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Sq < 0 || a->Skv < 0 || a->D <= 0)
-    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: negative or zero extent (B=%d Hq=%d Hkv=%d Sq=%d Skv=%d D=%d)",
-                     a->B, a->Hq, a->Hkv, a->Sq, a->Skv, a->D);
-  if (a->Hq % a->Hkv != 0)
-    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
-  if (a->dtype != HB_BF16 && a->dtype != HB_FP16)
-    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: dtype %d not supported (bf16, fp16)", a->dtype);
-  if (a->D != 64 && a->D != 128)
-    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: head_dim %d not supported (64 or 128)", a->D);
-  if (kFaScratchNeeded > kFaNoallocScratchBytes)
-    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: the kernel needs %zu bytes of scratch, the static array holds %zu",
-                     kFaScratchNeeded, kFaNoallocScratchBytes);
-  if (a->B == 0 || a->Sq == 0) return HB_OK;
-  if (a->Skv == 0) return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: Skv is 0 (softmax over an empty set)");
-  if (a->causal && a->Skv < a->Sq)
-    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: causal attention needs Skv >= Sq");
-  if (a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr)
-    return set_error(HB_ERR_BAD_ARG, "hb_fa_fwd_noalloc: q, k, v and o must be non-NULL");
-  const size_t es = dtype_size(a->dtype);
-  if ((reinterpret_cast<uintptr_t>(a->o) & 15u) != 0 || ((a->o_stride_s * es) & 15u) != 0 ||
-      ((a->o_stride_h * es) & 15u) != 0 || ((a->o_stride_b * es) & 15u) != 0)
-    return set_error(HB_ERR_ALIGN, "hb_fa_fwd_noalloc: o and its strides must be 16-byte aligned");
-  // The work list is indexed with 32-bit integers; this is the largest problem one launch takes.
-  const int nqb = (a->Sq + 2 * kTileM - 1) / (2 * kTileM);
-  const int npairs = (nqb + 1) / 2;
-  const long long total = (long long)a->B * a->Hq * npairs;
-  if (total > 0x7fffffffLL)
-    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: problem too large (%lld query blocks, limit %d)", total,
-                     0x7fffffff);
-
-  DeviceInfo info;
-  int rc = get_device_info_noalloc(&info);
-  if (rc != HB_OK) return rc;
-  if (info.device >= 64) return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: device index %d out of range", info.device);
-  if (g_fa_noalloc_ptr[info.device] == nullptr) {
-    // first call on this device: resolve the array's device address (no allocation)
+// Resolves (once per device, under the mutex) and returns the scratch array's device address
+// for the current device.  Allocates nothing.
+static int fa_noalloc_scratch(const char* who, int device, uint32_t** out) {
+  if (device < 0 || device >= 64) return set_error(HB_ERR_UNSUPPORTED, "%s: device index %d out of range", who, device);
+  std::lock_guard<std::mutex> lock(g_fa_mutex);
+  if (g_fa_noalloc_ptr[device] == nullptr) {
     void* ptr = nullptr;
     cudaError_t err = cudaGetSymbolAddress(&ptr, g_fa_noalloc_scratch);
     if (err != cudaSuccess || ptr == nullptr)
-      return set_error(HB_ERR_CUDA, "hb_fa_fwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
-    g_fa_noalloc_ptr[info.device] = ptr;
+      return set_error(HB_ERR_CUDA, "%s: cudaGetSymbolAddress failed: %s", who, cudaGetErrorString(err));
+    g_fa_noalloc_ptr[device] = ptr;
   }
-  uint32_t* status = static_cast<uint32_t*>(g_fa_noalloc_ptr[info.device]);
-  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  // the array keeps the previous call's contents: the status word must start at zero
-  HB_CUDA_CHECK(cudaMemsetAsync(status, 0, kFaScratchNeeded, stream));
+  *out = static_cast<uint32_t*>(g_fa_noalloc_ptr[device]);
+  return HB_OK;
+}
 
+static int fa_fwd_noalloc_impl(const hb_fa_args* a) {
+  bool empty = false;
+  int rc = fa_validate(a, "hb_fa_fwd_noalloc", /*allow_fp8=*/false, &empty);
+  if (rc != HB_OK || empty) return rc;
+  if (kFaScratchNeeded > kFaNoallocScratchBytes)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_fa_fwd_noalloc: the kernel needs %zu bytes of scratch, the static array holds %zu",
+                     kFaScratchNeeded, kFaNoallocScratchBytes);
+  DeviceInfo info;
+  rc = get_device_info_noalloc(&info);
+  if (rc != HB_OK) return rc;
+  uint32_t* status = nullptr;
+  rc = fa_noalloc_scratch("hb_fa_fwd_noalloc", info.device, &status);
+  if (rc != HB_OK) return rc;
+  // The status word is not cleared per call: the array starts out zero when the library is
+  // loaded, a kernel only ever moves the word from 0 to a code (first failure wins), and
+  // hb_status_word_noalloc hands it to the host and clears it.  A time-out therefore stays
+  // visible across later calls until it has been read.
   FaParams p;
-  memset(&p, 0, sizeof(p));
-  const CUtensorMapDataType dt =
-      a->dtype == HB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const uint32_t box[4] = {64, (uint32_t)kTileM, 1, 1};
-  {
-    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Sq, (uint64_t)a->Hq, (uint64_t)a->B};
-    const uint64_t str[3] = {(uint64_t)a->q_stride_s * es, (uint64_t)a->q_stride_h * es, (uint64_t)a->q_stride_b * es};
-    rc = encode_tensor_map(&p.tm_q, dt, 4, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != HB_OK) return rc;
+  rc = fa_fill_params(a, "hb_fa_fwd_noalloc", status, &p);
+  if (rc != HB_OK) return rc;
+  return dispatch_fa(a, p, std::min(p.total_pairs, info.sm_count), info.smem_optin);
+}
+
+// Reads (and then clears) the status word of the static scratch array on `stream`; waits for
+// that stream only.  No allocation: a 4-byte copy from the resolved symbol address.
+static int status_word_noalloc_impl(uint32_t* out, void* stream_v) {
+  if (out == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_status_word_noalloc: out is NULL");
+  DeviceInfo info;
+  int rc = get_device_info_noalloc(&info);
+  if (rc != HB_OK) return rc;
+  uint32_t* status = nullptr;
+  rc = fa_noalloc_scratch("hb_status_word_noalloc", info.device, &status);
+  if (rc != HB_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  HB_CUDA_CHECK(cudaMemcpyAsync(out, status, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+  HB_CUDA_CHECK(cudaStreamSynchronize(stream));
+  if (*out != 0) {
+    HB_CUDA_CHECK(cudaMemsetAsync(status, 0, sizeof(uint32_t), stream));
+    return set_error(HB_ERR_TIMEOUT, "hb_status_word_noalloc: %s", describe_status(*out));
   }
-  {
-    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Skv, (uint64_t)a->Hkv, (uint64_t)a->B};
-    const uint64_t str[3] = {(uint64_t)a->k_stride_s * es, (uint64_t)a->k_stride_h * es, (uint64_t)a->k_stride_b * es};
-    rc = encode_tensor_map(&p.tm_k, dt, 4, a->k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != HB_OK) return rc;
-  }
-  {
-    const uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Skv, (uint64_t)a->Hkv, (uint64_t)a->B};
-    const uint64_t str[3] = {(uint64_t)a->v_stride_s * es, (uint64_t)a->v_stride_h * es, (uint64_t)a->v_stride_b * es};
-    rc = encode_tensor_map(&p.tm_v, dt, 4, a->v, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != HB_OK) return rc;
-  }
-  p.o = a->o;
-  p.lse = a->lse;
-  p.status = status;
-  p.o_sb = a->o_stride_b;
-  p.o_sh = a->o_stride_h;
-  p.o_ss = a->o_stride_s;
-  p.B = a->B;
-  p.Hq = a->Hq;
-  p.Hkv = a->Hkv;
-  p.Sq = a->Sq;
-  p.Skv = a->Skv;
-  p.group = a->Hq / a->Hkv;
-  p.causal = a->causal ? 1 : 0;
-  p.nqb = nqb;
-  p.npairs = npairs;
-  p.total_pairs = (int)total;
-  p.nkv = (a->Skv + kTileN - 1) / kTileN;
-  const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->D);
-  p.scale_log2 = scale * 1.4426950408889634f;
-  p.out_scale = 1.0f;
-  const int grid = (int)std::min<long long>(total, info.sm_count);
-  if (a->dtype == HB_BF16) {
-    return a->D == 128 ? launch_fa<__nv_bfloat16, 128>(p, grid, info.smem_optin, stream)
-                       : launch_fa<__nv_bfloat16, 64>(p, grid, info.smem_optin, stream);
-  }
-  return a->D == 128 ? launch_fa<__half, 128>(p, grid, info.smem_optin, stream)
-                     : launch_fa<__half, 64>(p, grid, info.smem_optin, stream);
+  return HB_OK;
 }
 
 // ------------------------------------------------------------------------------------
@@ -436,6 +431,11 @@ int hb_debug_set_trace(void* ptr) {
 int hb_fa_fwd_noalloc(const hb_fa_args* args) {
   hb::clear_error();
   return hb::fa_fwd_noalloc_impl(args);
+}
+
+int hb_status_word_noalloc(uint32_t* out, void* stream) {
+  hb::clear_error();
+  return hb::status_word_noalloc_impl(out, stream);
 }
 
 int hb_debug_umma(int mode, const void* a, const void* b, float* out, int32_t kn, int32_t dtype, void* stream) {

@@ -20,6 +20,29 @@ int set_error(int code, const char* fmt, ...) {
 }
 void clear_error() { g_err[0] = '\0'; }
 
+const char* describe_status(uint32_t word) {
+  static thread_local char buf[160];
+  if (word == 0) {
+    snprintf(buf, sizeof(buf), "status word 0 (no bounded wait gave up)");
+  } else if ((word & 0xf00u) == 0x100u) {
+    // role ids: attention forward 1..5, GEMM 0x21.., H2O 0x31.., attention backward 0x41.., probes 0x70
+    const uint32_t role = word & 0xffu;
+    const char* kernel = role < 0x20 ? "attention forward" : role < 0x30 ? "GEMM" : role < 0x40 ? "H2O score"
+                         : role < 0x50 ? "attention backward" : "probe";
+    static const char* const kFa[] = {"?", "softmax", "correction", "MMA issuer", "TMA producer", "drain"};
+    static const char* const kOther[] = {"?", "TMA producer", "MMA issuer", "consumer", "drain"};
+    const char* name = role < 6 ? kFa[role] : ((role & 0xfu) < 5 && role < 0x50) ? kOther[role & 0xfu] : "?";
+    snprintf(buf, sizeof(buf),
+             "status word 0x%x: a bounded wait of the %s kernel gave up (role 0x%x, %s); that launch's outputs are incomplete",
+             word, kernel, role, name);
+  } else if (word == 0x200u) {
+    snprintf(buf, sizeof(buf), "status word 0x200: dynamic shared memory base was not 1024-byte aligned");
+  } else {
+    snprintf(buf, sizeof(buf), "status word 0x%x", word);
+  }
+  return buf;
+}
+
 static std::mutex g_mutex;
 static constexpr int kMaxDevices = 64;
 static DeviceState g_devices[kMaxDevices];
@@ -124,12 +147,14 @@ int hb_version(void) { return HB_VERSION; }
 const char* hb_last_error(void) { return hb::g_err; }
 
 int hb_status_word(uint32_t* out) {
+  hb::clear_error();
   if (out == nullptr) return hb::set_error(HB_ERR_BAD_ARG, "hb_status_word: out is NULL");
   hb::DeviceState* st = nullptr;
   int rc = hb::get_device_state(&st);
   if (rc != HB_OK) return rc;
   HB_CUDA_CHECK(cudaDeviceSynchronize());
   HB_CUDA_CHECK(cudaMemcpy(out, st->status_word, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  if (*out != 0) return hb::set_error(HB_ERR_TIMEOUT, "hb_status_word: %s", hb::describe_status(*out));
   return HB_OK;
 }
 

@@ -15,6 +15,10 @@ namespace hb {
 int set_error(int code, const char* fmt, ...);
 void clear_error();
 
+// Human-readable form of a device status word (0x100 | role: a bounded wait of that role ran out;
+// 0x200: shared memory base misaligned).  Returns a pointer to a thread-local buffer.
+const char* describe_status(uint32_t word);
+
 #define HB_CUDA_CHECK(expr)                                                                   \
   do {                                                                                        \
     cudaError_t err__ = (expr);                                                               \

@@ -110,12 +110,24 @@ int hb_fa_fwd(const hb_fa_args* args);
  * (cudaGetSymbolAddress, with that device current).  Make that first call outside any
  * stream capture.  Limits: bf16 / fp16 only; at most 2^31-1 query blocks of 256 rows
  * (B * Hq * ceil(ceil(Sq/256)/2)) per call, larger problems are rejected with
- * HB_ERR_UNSUPPORTED.  All calls on a device share the one array, which keeps the last
- * call's contents; each call clears its status word on `stream` before the kernel runs,
- * so two calls whose kernels overlap on the GPU (different streams) race on it — issue
- * them on one stream or order them with events.
+ * HB_ERR_UNSUPPORTED.  All calls on a device share the one array, which keeps its contents
+ * from call to call: the status word in it starts at zero when the library is loaded, a
+ * kernel only moves it from zero to a failure code (the first failure wins) and only
+ * hb_status_word_noalloc clears it.  Calls whose kernels overlap on the GPU (different
+ * streams) therefore race on that word: a failure cannot be attributed to one of them —
+ * issue them on one stream or order them with events if that matters.
  */
 int hb_fa_fwd_noalloc(const hb_fa_args* args);
+
+/*
+ * Status word of the hb_fa_fwd_noalloc path on the current device (hb_status_word reads a
+ * different, allocated word and allocates on first use, so a host that may not allocate
+ * cannot call it).  Copies the word out of the static array on `stream`, waits for that
+ * stream, and if it is non-zero clears it and returns HB_ERR_TIMEOUT with hb_last_error()
+ * naming the kernel role whose wait gave up.  Allocates nothing.  No counterpart in the
+ * reference.
+ */
+int hb_status_word_noalloc(uint32_t* out, void* stream);
 
 /*
  * H2O score:  score[b,h,k] = sum_q exp(scaled masked score[q,k] - LSE[q])
@@ -282,7 +294,9 @@ int hb_row_softmax(const void* x, void* y, int64_t rows, int32_t cols, int64_t l
                    float scale, int32_t dtype, void* stream);
 
 /* Device-side status word of the current device (0 = no bounded wait ever gave up);
- * reading it synchronises the device. */
+ * reading it synchronises the device.  *out always receives the word; the return value is
+ * HB_OK when it is zero and HB_ERR_TIMEOUT otherwise (hb_last_error() then names the kernel
+ * and the role whose wait ran out; the outputs of that launch are incomplete). */
 int hb_status_word(uint32_t* out);
 
 /* Library / device information. */

@@ -2,7 +2,8 @@
 allocate device memory (fixed memory budget, allocation forbidden after start-up, or a
 call site where cudaMalloc is not permitted).  It must give the same result as
 hb_fa_fwd while keeping its scratch (the kernel's status word) in a static device array
-of the library.
+of the library, and its status must be readable without an allocation
+(hb_status_word_noalloc).
 
 The file sorts last on purpose: if it fails under ``pytest -x`` every other test has run.
 It passes both alone in a fresh process (the first library call is then the no-alloc one)
@@ -13,6 +14,8 @@ import math
 
 import pytest
 import torch
+
+from oracle import attention_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -33,6 +36,12 @@ def _args(_lib, q, k, v, out, lse, causal):
     return a
 
 
+def _status(built_lib):
+    w = C.c_uint32(0xFFFFFFFF)
+    rc = built_lib.hb_status_word_noalloc(C.byref(w), torch.cuda.current_stream().cuda_stream)
+    return rc, int(w.value)
+
+
 def test_noalloc_entry_matches_hb_fa_fwd_twice_in_a_row(built_lib):
     from heddle_b200 import _lib, ops
 
@@ -49,20 +58,30 @@ def test_noalloc_entry_matches_hb_fa_fwd_twice_in_a_row(built_lib):
         rc = built_lib.hb_fa_fwd_noalloc(C.byref(a))
         assert rc == _lib.HB_OK, built_lib.hb_last_error()
         torch.cuda.synchronize()
-        ref_out, ref_lse = ops.fa_fwd(q, k, v, causal=causal, return_lse=True)  # the existing entry point
-        torch.cuda.synchronize()
+        assert _status(built_lib) == (_lib.HB_OK, 0)
+        # against the CPU oracle (the pinned restatement of the reference's eager graph) ...
+        ref, ref_l = O.attention_eager(q.cpu(), k.cpu(), v.cpu(), causal=causal)
         assert not torch.isnan(out.float()).any(), f"call {call}: output not fully written"
-        assert (out.float() - ref_out.float()).abs().max().item() <= 2e-2
-        assert (lse - ref_lse).abs().max().item() <= 1e-3
-        # same kernel, same inputs: in fact bit-identical
+        assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
+        assert (lse.cpu() - ref_l).abs().max().item() <= 1e-3
+        # ... and against the existing entry point: same kernel, same inputs, in fact bit-identical
+        ref_out, ref_lse = ops.fa_fwd(q, k, v, causal=causal, return_lse=True)
+        torch.cuda.synchronize()
         assert torch.equal(out, ref_out) and torch.equal(lse, ref_lse)
 
-    # immediately repeated call on the same buffers (the shared scratch keeps the previous contents)
+    # immediately repeated calls on the same buffers (the shared scratch keeps its contents), and
+    # the property the entry point exists for: the device's free memory does not move
     out2 = torch.empty_like(out)
     a2 = _args(_lib, q, k, v, out2, lse, causal)
-    assert built_lib.hb_fa_fwd_noalloc(C.byref(a2)) == _lib.HB_OK
-    assert built_lib.hb_fa_fwd_noalloc(C.byref(a2)) == _lib.HB_OK
+    assert built_lib.hb_fa_fwd_noalloc(C.byref(a2)) == _lib.HB_OK  # set-up done before measuring
     torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(4):
+        assert built_lib.hb_fa_fwd_noalloc(C.byref(a2)) == _lib.HB_OK
+    assert _status(built_lib) == (_lib.HB_OK, 0)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "hb_fa_fwd_noalloc / hb_status_word_noalloc changed the device's free memory"
     assert torch.equal(out2, out)
 
 
@@ -79,3 +98,17 @@ def test_noalloc_entry_rejects_what_it_cannot_take(built_lib):
     a = _args(_lib, q, q, q, torch.empty_like(q), lse, False)
     a.dtype = _lib.HB_FP8_E4M3
     assert built_lib.hb_fa_fwd_noalloc(C.byref(a)) == _lib.HB_ERR_UNSUPPORTED
+    # misaligned output, misaligned lse
+    a = _args(_lib, q, q, q, torch.empty_like(q), lse, False)
+    a.o = a.o + 2
+    assert built_lib.hb_fa_fwd_noalloc(C.byref(a)) == _lib.HB_ERR_ALIGN
+    a = _args(_lib, q, q, q, torch.empty_like(q), lse, False)
+    a.lse = a.lse + 2
+    assert built_lib.hb_fa_fwd_noalloc(C.byref(a)) == _lib.HB_ERR_ALIGN
+    # causal with fewer keys than queries
+    a = _args(_lib, q, q, q, torch.empty_like(q), lse, True)
+    a.Skv = 64
+    assert built_lib.hb_fa_fwd_noalloc(C.byref(a)) == _lib.HB_ERR_UNSUPPORTED
+    assert b"Skv >= Sq" in built_lib.hb_last_error()
+    # the status reader needs somewhere to write
+    assert built_lib.hb_status_word_noalloc(None, None) == _lib.HB_ERR_BAD_ARG
