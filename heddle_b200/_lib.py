@@ -23,6 +23,9 @@ HB_BF16 = 0
 HB_FP16 = 1
 HB_FP8_E4M3 = 2
 
+HB_W_NK = 0
+HB_W_KN = 1
+
 HB_QUERY_SM_COUNT = 0
 HB_QUERY_SMEM_OPTIN = 1
 HB_QUERY_CC = 2
@@ -89,6 +92,9 @@ class GemmArgs(C.Structure):
         ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
         ("rope_seq", C.c_int32), ("head_dim", C.c_int32), ("rope_cols", C.c_int32),
         ("stream", C.c_void_p),
+        ("batch", C.c_int32), ("w_layout", C.c_int32),
+        ("a_batch_stride", C.c_int64), ("w_batch_stride", C.c_int64), ("o_batch_stride", C.c_int64),
+        ("r_batch_stride", C.c_int64),
     ]
 
 

@@ -61,14 +61,30 @@ static int gemm_impl(const hb_gemm_args* a) {
     if ((reinterpret_cast<uintptr_t>(a->rope_cos) & 15) != 0 || (reinterpret_cast<uintptr_t>(a->rope_sin) & 15) != 0)
       return set_error(HB_ERR_ALIGN, "hb_gemm_epilogue: ROPE tables need 16-byte alignment");
   }
+  const int batch = a->batch > 0 ? a->batch : 1;
+  const bool w_kn = a->w_layout == HB_W_KN;
+  if (a->w_layout != HB_W_NK && a->w_layout != HB_W_KN)
+    return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: unknown w_layout %d", a->w_layout);
+  if (w_kn && epi_class != kEpiPlain)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: SWIGLU / ROPE need the weight in [N, K] layout");
+  if (batch > 1 && epi_class == kEpiRope)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: ROPE is not defined for batched products");
   if (a->M == 0) return HB_OK;
   if (a->a == nullptr || a->w == nullptr || a->out == nullptr)
     return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: a, w and out must be non-NULL");
   if ((a->K % 8) || (n_out % 8) || (a->lda % 8) || (a->ldw % 8) || (a->ldo % 8) ||
       (a->residual != nullptr && (a->ldr % 8)))
     return set_error(HB_ERR_ALIGN, "hb_gemm_epilogue: K, N_out and the leading dimensions must be multiples of 8");
-  if (a->lda < a->K || a->ldw < a->K || a->ldo < n_out || (a->residual != nullptr && a->ldr < n_out))
+  if (a->lda < a->K || a->ldw < (w_kn ? a->N : a->K) || a->ldo < n_out || (a->residual != nullptr && a->ldr < n_out))
     return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: a leading dimension is smaller than its row");
+  const long long w_rows = w_kn ? a->K : a->N;
+  // batch strides (elements); 0 selects densely packed batches
+  const long long a_bs = a->a_batch_stride ? a->a_batch_stride : (long long)a->M * a->lda;
+  const long long w_bs = a->w_batch_stride ? a->w_batch_stride : w_rows * a->ldw;
+  const long long o_bs = a->o_batch_stride ? a->o_batch_stride : (long long)a->M * a->ldo;
+  const long long r_bs = a->r_batch_stride ? a->r_batch_stride : (long long)a->M * a->ldr;
+  if (batch > 1 && ((a_bs % 8) || (w_bs % 8) || (o_bs % 8) || (a->residual != nullptr && (r_bs % 8))))
+    return set_error(HB_ERR_ALIGN, "hb_gemm_epilogue: batch strides must be multiples of 8 elements");
   if (!aligned16(a->a) || !aligned16(a->w) || !aligned16(a->out) || !aligned16(a->residual) || !aligned16(a->bias))
     return set_error(HB_ERR_ALIGN, "hb_gemm_epilogue: pointers must be 16-byte aligned");
 
@@ -79,17 +95,24 @@ static int gemm_impl(const hb_gemm_args* a) {
   GemmParams p;
   memset(&p, 0, sizeof(p));
   const CUtensorMapDataType dt = a->dtype == HB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const uint32_t box[2] = {(uint32_t)kGemmBK, 128};
   {
-    const uint64_t dims[2] = {(uint64_t)a->K, (uint64_t)a->M};
-    const uint64_t str[1] = {(uint64_t)a->lda * 2};
-    rc = encode_tensor_map(&p.tm_a, dt, 2, a->a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    const uint32_t box[3] = {(uint32_t)kGemmBK, 128, 1};
+    const uint64_t dims[3] = {(uint64_t)a->K, (uint64_t)a->M, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)a->lda * 2, (uint64_t)a_bs * 2};
+    rc = encode_tensor_map(&p.tm_a, dt, 3, a->a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HB_OK) return rc;
   }
-  {
-    const uint64_t dims[2] = {(uint64_t)a->K, (uint64_t)a->N};
-    const uint64_t str[1] = {(uint64_t)a->ldw * 2};
-    rc = encode_tensor_map(&p.tm_w, dt, 2, a->w, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (w_kn) {
+    const uint32_t box[3] = {64, (uint32_t)kGemmBK, 1};  // 64 columns (128 bytes) x 64 k-rows
+    const uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)a->K, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)a->ldw * 2, (uint64_t)w_bs * 2};
+    rc = encode_tensor_map(&p.tm_w, dt, 3, a->w, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+  } else {
+    const uint32_t box[3] = {(uint32_t)kGemmBK, 128, 1};
+    const uint64_t dims[3] = {(uint64_t)a->K, (uint64_t)a->N, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)a->ldw * 2, (uint64_t)w_bs * 2};
+    rc = encode_tensor_map(&p.tm_w, dt, 3, a->w, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HB_OK) return rc;
   }
   p.out = a->out;
@@ -107,9 +130,15 @@ static int gemm_impl(const hb_gemm_args* a) {
   p.tile_cols = epi_class == kEpiSwiglu ? 128 : kGemmBN;
   p.tiles_m = (a->M + kGemmBM - 1) / kGemmBM;
   p.tiles_n = (n_out + p.tile_cols - 1) / p.tile_cols;
-  const long long tiles = (long long)p.tiles_m * p.tiles_n;
-  if (tiles > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: too many tiles");
+  p.tiles_per_batch = p.tiles_m * p.tiles_n;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n * batch;
+  if (tiles > 0x7fffffffLL || (long long)batch * a->M > 0x7fffffffLL)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: too many tiles");
   p.num_tiles = (int)tiles;
+  p.batch = batch;
+  p.w_kn = w_kn ? 1 : 0;
+  p.o_batch_stride = o_bs;
+  p.r_batch_stride = r_bs;
   p.k_steps = (a->K + kGemmBK - 1) / kGemmBK;
   p.act = (a->epilogue >= HB_EPI_SILU && a->epilogue <= HB_EPI_TANH) ? a->epilogue : kActNone;
   p.rope_seq = a->rope_seq;

@@ -14,6 +14,13 @@
 //   warps 2-9  epilogue, two warpgroups: a thread owns one row and half of the tile's columns;
 //              TMEM -> registers -> epilogue math -> 16-byte global stores
 //
+// Batched products (torch.bmm, the reference's _build_bmm_kernel, Heddle/heddle/frontend/backend.py:491-517)
+// put the batch index into the tile list: the tensor maps are 3-D (K, rows, batch), a tile is
+// (batch, m, n).  The second operand may also be given as [K, N] row-major (what torch.mm / bmm and
+// the reference's _build_gemm_kernel, backend.py:227-252, take): its tiles are then loaded as four
+// [64 k-rows x 64 columns] slabs and consumed through an MN-major shared-memory descriptor, so no
+// transposed copy is made for that layout either.
+//
 // Epilogue classes:
 //   PLAIN   row_scale, bias, unary activation, residual              (256 output columns / tile)
 //   SWIGLU  B tile = 128 rows of Wg and the matching 128 rows of Wu;  out = silu(g) * u
@@ -54,6 +61,10 @@ struct alignas(64) GemmParams {
   int act;
   int rope_seq, head_dim, rope_cols;
   int w_row2_offset;  // SWIGLU: first row of Wu inside the stacked weight
+  int batch;          // number of independent products (>= 1)
+  int tiles_per_batch;
+  int w_kn;           // 1: the second operand is [K, N] row-major
+  long long o_batch_stride, r_batch_stride;  // elements between consecutive batches of out / residual
 };
 
 struct GemmSmem {
@@ -66,7 +77,9 @@ struct GemmSmem {
   uint32_t abort_flag;
 };
 
-__device__ __forceinline__ void gemm_tile_coords(const GemmParams& p, int t, int& m_t, int& n_t) {
+__device__ __forceinline__ void gemm_tile_coords(const GemmParams& p, int t, int& m_t, int& n_t, int& b) {
+  b = t / p.tiles_per_batch;
+  t -= b * p.tiles_per_batch;
   const int per_group = kGemmGroupM * p.tiles_n;
   const int g = t / per_group;
   const int first_m = g * kGemmGroupM;
@@ -128,14 +141,16 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 
 // Stores 8 consecutive output values of one row (16 bytes), adding the residual if any.
 template <typename T>
-__device__ __forceinline__ void store8(const GemmParams& p, int row, int col, float (&v)[8]) {
+__device__ __forceinline__ void store8(const GemmParams& p, int b, int row, int col, float (&v)[8]) {
   if (p.residual != nullptr) {
     float r[8];
-    unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + (long long)row * p.ldr + col), r);
+    unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + b * p.r_batch_stride +
+                                               (long long)row * p.ldr + col),
+               r);
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] += r[i];
   }
-  *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + (long long)row * p.ldo + col) = pack8<T>(v);
+  *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + b * p.o_batch_stride + (long long)row * p.ldo + col) = pack8<T>(v);
 }
 
 template <typename T>
@@ -147,11 +162,11 @@ __device__ __forceinline__ void load_bias8(const GemmParams& p, int col, float (
 // warp's TMEM lane offset and the accumulator buffer's first column.  Two warpgroups share a
 // tile: `part` (0 or 1) selects this thread's half of the output columns.
 template <typename T, int EPI>
-__device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t tacc, int m0, int n0, int row_in_tile,
-                                                  int part) {
+__device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t tacc, int b, int m0, int n0,
+                                                  int row_in_tile, int part) {
   const int row = m0 + row_in_tile;
   const bool row_ok = row < p.M;
-  const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
+  const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[(long long)b * p.M + row] : 1.0f;
 
   if constexpr (EPI == kEpiPlain) {
 #pragma unroll 1
@@ -176,7 +191,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = apply_act(v[e], p.act);
-        store8<T>(p, row, col + g * 8, v);
+        store8<T>(p, b, row, col + g * 8, v);
       }
     }
   } else if constexpr (EPI == kEpiSwiglu) {
@@ -210,7 +225,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = v[e] * (1.0f / (1.0f + __expf(-v[e]))) * u[e];
-        store8<T>(p, row, col + g * 8, v);
+        store8<T>(p, b, row, col + g * 8, v);
       }
     }
   } else {  // kEpiRope
@@ -267,8 +282,8 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
               x2[e] = b * cs[e] + a * sn[e];
             }
           }
-          store8<T>(p, row, col + g * 8, x1);
-          store8<T>(p, row, col + half + g * 8, x2);
+          store8<T>(p, b, row, col + g * 8, x1);
+          store8<T>(p, b, row, col + half + g * 8, x2);
         }
       }
     }
@@ -315,8 +330,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       uint32_t st = 0, phase = 1;  // "empty" barriers start out free
       bool ok = true;
       for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
-        int m_t, n_t;
-        gemm_tile_coords(p, t, m_t, n_t);
+        int m_t, n_t, b;
+        gemm_tile_coords(p, t, m_t, n_t, b);
         const int m0 = m_t * kGemmBM;
         const int n0 = n_t * p.tile_cols;
         const int row_b0 = n0;
@@ -327,9 +342,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             break;
           }
           mbar_arrive_expect_tx(&s.full[st], kStageBytes);
-          tma_load_2d(s.a[st], &p.tm_a, &s.full[st], ks * kGemmBK, m0);
-          tma_load_2d(s.b[st], &p.tm_w, &s.full[st], ks * kGemmBK, row_b0);
-          tma_load_2d(s.b[st] + 128 * kGemmBK * 2, &p.tm_w, &s.full[st], ks * kGemmBK, row_b1);
+          tma_load_3d(s.a[st], &p.tm_a, &s.full[st], ks * kGemmBK, m0, b);
+          if (p.w_kn) {
+            // [K, N] operand: four slabs of 64 k-rows x 64 columns (128 bytes per row)
+#pragma unroll
+            for (int i = 0; i < kGemmBN / 64; ++i)
+              tma_load_3d(s.b[st] + i * (kGemmBK * 128), &p.tm_w, &s.full[st], n0 + i * 64, ks * kGemmBK, b);
+          } else {
+            tma_load_3d(s.b[st], &p.tm_w, &s.full[st], ks * kGemmBK, row_b0, b);
+            tma_load_3d(s.b[st] + 128 * kGemmBK * 2, &p.tm_w, &s.full[st], ks * kGemmBK, row_b1, b);
+          }
           if (++st == kGemmStages) {
             st = 0;
             phase ^= 1;
@@ -342,9 +364,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     if (run) {
       // ---------------- MMA issuer: the whole warp runs the loop (operands stay warp-uniform),
       // one elected lane issues ----------------
-      constexpr uint32_t idesc = make_idesc(Pack2<T>::kFormat, kGemmBM, kGemmBN, 0, 0);
+      constexpr uint32_t idesc_nk = make_idesc(Pack2<T>::kFormat, kGemmBM, kGemmBN, 0, 0);
+      constexpr uint32_t idesc_kn = make_idesc(Pack2<T>::kFormat, kGemmBM, kGemmBN, 0, 1);
       constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
       constexpr uint32_t kLbo = (16u >> 4) << 16;
+      // [K, N] operand (MN-major): the next 64 columns live one slab (64 k-rows x 128 bytes) further,
+      // a K = 16 step advances by 16 rows of 128 bytes
+      constexpr uint32_t kLboKn = ((kGemmBK * 128u) >> 4) << 16;
+      const uint32_t idesc = p.w_kn ? idesc_kn : idesc_nk;
+      const uint32_t b_lbo = p.w_kn ? kLboKn : kLbo;
+      const uint32_t b_step = p.w_kn ? (16u * 128u >> 4) : 2u;
       const bool leader = elect_one();
       uint32_t stage = 0, phase = 0, tile_i = 0;
       bool ok = true;
@@ -362,12 +391,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             break;
           }
           tc_fence_after();
-          const uint32_t a_lo = (smem_u32(s.a[stage]) >> 4) | kLbo, b_lo = (smem_u32(s.b[stage]) >> 4) | kLbo;
+          const uint32_t a_lo = (smem_u32(s.a[stage]) >> 4) | kLbo, b_lo = (smem_u32(s.b[stage]) >> 4) | b_lbo;
           if (leader) {
 #pragma unroll
             for (int kk = 0; kk < kGemmBK / 16; ++kk) {
               umma_ss_f16(d_tmem, (static_cast<uint64_t>(kDescHi) << 32) | (a_lo + kk * 2),
-                          (static_cast<uint64_t>(kDescHi) << 32) | (b_lo + kk * 2), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                          (static_cast<uint64_t>(kDescHi) << 32) | (b_lo + kk * b_step), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(&s.empty[stage]);
           }
@@ -391,12 +420,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     uint32_t tile_i = 0;
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++tile_i) {
-      int m_t, n_t;
-      gemm_tile_coords(p, t, m_t, n_t);
+      int m_t, n_t, b;
+      gemm_tile_coords(p, t, m_t, n_t, b);
       const uint32_t acc = tile_i & 1;
       if (!mbar_wait_warp(&s.acc_full[acc], (tile_i >> 1) & 1, ctx, kGemmRoleEpi)) break;
       tc_fence_after();
-      gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, m_t * kGemmBM, n_t * p.tile_cols,
+      gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, b, m_t * kGemmBM, n_t * p.tile_cols,
                                 quarter * 32 + lane, (warp - 2) >> 2);
       tc_fence_before();
       __syncwarp();

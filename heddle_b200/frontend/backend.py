@@ -31,9 +31,11 @@ from typing import List, Optional, Tuple
 
 import torch
 import torch.fx as fx
-from torch.fx import replace_pattern
+from torch.fx.subgraph_rewriter import replace_pattern_with_filters
 
 from .. import ops
+from .decomposition import recompose_softmax
+from .normalization import canonicalize_ops
 from .patterns import (
     _heuristic_config,
     scaled_dot_product_attention_pattern,
@@ -101,6 +103,38 @@ def _tilelang_h2o_attention(q, k, v, is_causal=True, scale=None):
     out, lse = ops.fa_fwd(q, k, v, causal=bool(is_causal), softmax_scale=sm, return_lse=True)
     score = ops.h2o_score(q, k, lse, causal=bool(is_causal), softmax_scale=sm)
     return out, score
+
+
+# ----------------------------------------------------------------------------------------
+# per-op GEMM leaves with the reference's names.  Its rewriters that would insert them are never
+# called (backend.py:1487-1491); they are kept as the leaf-node surface and are what the
+# matmul / bmm lowering of the fusion pass inserts for products that are not nn.Linear calls.
+# ----------------------------------------------------------------------------------------
+@torch.fx.wrap
+def _tilelang_gemm_wrapper(a, b):
+    """C = A . B for a [M, K] (or (..., K)) and b [K, N] (backend.py:258-272); B is read in place."""
+    return ops.gemm(a, b)
+
+
+@torch.fx.wrap
+def _tilelang_linear_wrapper(input_nd, weight_2d):
+    """(..., K) x nn.Linear weight [N, K] -> (..., N) (backend.py:275-300); no transposed weight copy."""
+    return ops.gemm_epilogue(input_nd, weight_2d, "none")
+
+
+@torch.fx.wrap
+def _tilelang_bmm_wrapper(a, b):
+    """Batched product [B, M, K] x [B, K, N] in one launch (backend.py:523-536)."""
+    return ops.bmm(a, b)
+
+
+@torch.fx.wrap
+def _tilelang_swiglu_wrapper(x, w_gate, w_up):
+    """silu(x @ w_gate.T) * (x @ w_up.T) with the activation inside the GEMM epilogue
+    (backend.py:572-598 runs one GEMM on the concatenated weights and the product in PyTorch)."""
+    from .fusion import hb_swiglu
+
+    return hb_swiglu(x, w_gate, w_up)
 
 
 _ATTENTION_LEAVES = (_tilelang_sdpa_direct, _tilelang_h2o_attention, tilelang_flash_attn_wrapper,
@@ -211,6 +245,42 @@ def _constant_scale(node: fx.Node) -> Optional[Tuple[fx.Node, float]]:
     return None
 
 
+def _dtype_of(node):
+    if isinstance(node, fx.Node):
+        val = node.meta.get("example_value", node.meta.get("val", None))
+        if val is not None and hasattr(val, "dtype"):
+            return val.dtype
+        tm = node.meta.get("tensor_meta", None)
+        if tm is not None:
+            return tm.dtype
+    return None
+
+
+def _attention_unsupported(q, k, v, causal_top_left: bool = False) -> Optional[str]:
+    """Why the sm_100a attention kernels cannot take these operands (None = they can).  Decided from
+    the shapes and dtypes recorded in the nodes' metadata; a node without metadata cannot be judged and
+    is let through, as the reference does for every node (backend.py:906-943 checks nothing)."""
+    shapes = [_shape_of(t) for t in (q, k, v)]
+    dtypes = [_dtype_of(t) for t in (q, k, v)]
+    if any(s is None for s in shapes) or any(d is None for d in dtypes):
+        return None
+    qs, ks, vs = shapes
+    if any(len(s) != 4 for s in shapes):
+        return f"operands are not 4-D (B, H, S, D): {qs}, {ks}, {vs}"
+    if dtypes[0] not in (torch.bfloat16, torch.float16) or dtypes[1] != dtypes[0] or dtypes[2] != dtypes[0]:
+        return f"dtypes {dtypes} (the kernels take bf16 or fp16, the same for q, k, v)"
+    if qs[3] not in (64, 128) or ks[3] != qs[3] or vs[3] != qs[3]:
+        return f"head_dim {qs[3]} / {ks[3]} / {vs[3]} (64 or 128, equal for q, k, v)"
+    if ks[:3] != vs[:3] or ks[0] != qs[0] or ks[1] == 0 or qs[1] % ks[1] != 0:
+        return f"inconsistent shapes q {qs}, k {ks}, v {vs}"
+    if causal_top_left and qs[2] != ks[2]:
+        # F.scaled_dot_product_attention(is_causal=True) aligns its mask to the top-left corner
+        # (tril(ones(L, S))); the kernel's causal mask is aligned to the end of the keys
+        # (key <= query + Skv - Sq, the reference's past_len rule).  The two agree only for Sq == Skv.
+        return f"is_causal=True with Sq={qs[2]} != Skv={ks[2]}: mask alignments differ"
+    return None
+
+
 class _AttentionMatch:
     __slots__ = ("q", "k", "v", "scale", "causal", "softmax", "pv", "sum_user")
 
@@ -276,6 +346,10 @@ def _match_attention(sm: fx.Node) -> Optional[_AttentionMatch]:
             return None  # the probabilities escape some other way (dropout, return value, ...)
     if pv is None or not isinstance(pv.args[1], fx.Node):
         return None
+    why = _attention_unsupported(q, k, pv.args[1])
+    if why is not None:
+        log.info("expanded attention at %s keeps its eager form: %s", sm.name, why)
+        return None
     m = _AttentionMatch()
     m.q, m.k, m.v, m.scale, m.causal, m.softmax, m.pv, m.sum_user = q, k, pv.args[1], scale, causal, sm, pv, sum_user
     return m
@@ -309,6 +383,10 @@ def _replace_sdpa_op(gm: fx.GraphModule) -> bool:
         if mask is not None or dropout not in (0, 0.0) or not isinstance(is_causal, bool) \
                 or not (scale is None or isinstance(scale, (int, float))):
             log.info("SDPA node %s keeps its eager form (mask / dropout / dynamic scale)", node.name)
+            continue
+        why = _attention_unsupported(q, k, v, causal_top_left=bool(is_causal))
+        if why is not None:
+            log.info("SDPA node %s keeps its eager form: %s", node.name, why)
             continue
         with gm.graph.inserting_before(node):
             new = gm.graph.call_function(_tilelang_sdpa_direct, (q, k, v),
@@ -379,6 +457,24 @@ def try_fuse_h2o_attention(gm: fx.GraphModule) -> bool:
     return fused
 
 
+def _bshd_match_supported(match, original_graph, pattern_graph) -> bool:
+    """Filter for the (B, S, H, D) pattern: the matched q, k, v must be operands the kernels take."""
+    nodes = list(match.placeholder_nodes)[:3]
+    if len(nodes) < 3 or not all(isinstance(n, fx.Node) for n in nodes):
+        return True
+    shapes = [_shape_of(n) for n in nodes]
+    dtypes = [_dtype_of(n) for n in nodes]
+    if any(s is None or len(s) != 4 for s in shapes) or any(d is None for d in dtypes):
+        return all(s is None for s in shapes)  # no metadata: cannot judge; wrong rank: refuse
+    (qb, qs_, qh, qd), (kb, ks_, kh, kd), (vb, vs_, vh, vd) = shapes
+    ok = (dtypes[0] in (torch.bfloat16, torch.float16) and dtypes[1] == dtypes[0] and dtypes[2] == dtypes[0]
+          and qd in (64, 128) and kd == qd and vd == qd and (kb, ks_, kh) == (vb, vs_, vh) and kb == qb
+          and kh > 0 and qh % kh == 0)
+    if not ok:
+        log.info("BSHD attention pattern keeps its eager form: shapes %s dtypes %s", shapes, dtypes)
+    return ok
+
+
 def _prefer_bshd_outputs(gm: fx.GraphModule) -> None:
     """An attention leaf whose only consumer is ``transpose(1, 2)`` writes its result in that layout."""
     for node in gm.graph.nodes:
@@ -416,12 +512,18 @@ def tilelang_backend(gm: torch.fx.GraphModule, example_inputs: List[torch.Tensor
     if os.environ.get("TILELANG_FRONTEND_PRINT_GRAPH", "0").strip() == "1":
         print(gm.print_readable(print_output=False))
 
+    # the matchers below see one spelling of the arithmetic: in-place operators made functional where
+    # that is unobservable, hand-written safe-softmax chains folded into softmax nodes
+    canonicalize_ops(gm)
+    recompose_softmax(gm)
+
     fused_attention = False
     if enable_h2o:
         fused_attention = try_fuse_h2o_attention(gm) or fused_attention
     if enable_fa:
         before = sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target is tilelang_flash_attn_wrapper)
-        replace_pattern(gm, scaled_dot_product_attention_pattern, tilelang_flash_attn_replacement)
+        replace_pattern_with_filters(gm, scaled_dot_product_attention_pattern, tilelang_flash_attn_replacement,
+                                     match_filters=[_bshd_match_supported])
         after = sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target is tilelang_flash_attn_wrapper)
         fused_sdpa = after > before
         fused_sdpa = _replace_sdpa_op(gm) or fused_sdpa

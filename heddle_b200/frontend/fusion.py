@@ -17,7 +17,9 @@ sibling projections (Q, K, V) merged into one GEMM on stacked weights.
 """
 from __future__ import annotations
 
+import collections
 import operator
+import weakref
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -31,32 +33,77 @@ _ACT_NAMES = {"silu": "silu", "relu": "relu", "sigmoid": "sigmoid", "tanh": "tan
 # ----------------------------------------------------------------------------------------
 # leaves
 # ----------------------------------------------------------------------------------------
-_prepared: Dict[Tuple, torch.Tensor] = {}
+class _PreparedWeights:
+    """Cache of stacked / gamma-folded weight operands, one entry per group of source tensors.
+
+    An entry is keyed by the identity of its source tensors and remembers their storage addresses
+    and versions: a hit requires the very same tensor objects, unchanged.  An in-place update
+    (optimizer step), a ``.data`` swap or a reload replaces the entry instead of adding one, and a
+    finalizer drops the entry when a source tensor dies, so the cache holds at most one operand per
+    live weight group (and never more than ``capacity``)."""
+
+    def __init__(self, capacity: int = 256):
+        self.capacity = capacity
+        self._entries: "collections.OrderedDict[Tuple[int, ...], Tuple]" = collections.OrderedDict()
+
+    @staticmethod
+    def _state(t: torch.Tensor) -> Tuple:
+        try:
+            version = t._version
+        except RuntimeError:  # inference-mode tensors do not track versions
+            version = -1
+        return (t.data_ptr(), version, tuple(t.shape), tuple(t.stride()), t.dtype, str(t.device))
+
+    def get(self, sources, build):
+        key = tuple(id(t) for t in sources)
+        state = tuple(self._state(t) for t in sources)
+        entry = self._entries.get(key)
+        if entry is not None:
+            refs, old_state, value = entry
+            if old_state == state and all(r() is t for r, t in zip(refs, sources)):
+                self._entries.move_to_end(key)
+                return value
+        value = build()
+
+        def drop(_ref, key=key, entries=self._entries):
+            entries.pop(key, None)
+
+        self._entries[key] = (tuple(weakref.ref(t, drop) for t in sources), state, value)
+        self._entries.move_to_end(key)
+        while len(self._entries) > self.capacity:
+            self._entries.popitem(last=False)
+        return value
+
+    def __len__(self) -> int:
+        return len(self._entries)
+
+    def clear(self) -> None:
+        self._entries.clear()
 
 
-def _key(*tensors: Optional[torch.Tensor]) -> Tuple:
-    return tuple(None if t is None else (t.data_ptr(), t._version, tuple(t.shape), t.dtype) for t in tensors)
+_prepared = _PreparedWeights()
 
 
 def _prepare(ws, gamma: Optional[torch.Tensor]) -> torch.Tensor:
     """The GEMM's weight operand: the given nn.Linear weights stacked along the rows ([Wg; Wu],
     [Wq; Wk; Wv]; the reference concatenates likewise, codegen.py:1146-1152) with the RMSNorm
-    weight folded into the columns, built once per (weights, gamma) version by hb_prepare_weight."""
+    weight folded into the columns, built once per state of (weights, gamma) by hb_prepare_weight
+    (the reference caches its transposed weight by ``data_ptr()`` alone, codegen.py:1128-1129)."""
     ws = tuple(ws)
     if len(ws) == 1 and gamma is None:
         return ws[0]
-    k = _key(*ws, gamma)
-    hit = _prepared.get(k)
-    if hit is None:
+
+    def build():
         if len(ws) <= 4 and all(w.shape[1] % 8 == 0 and w.dtype in (torch.bfloat16, torch.float16) for w in ws):
-            hit = ops.prepare_weight(ws, gamma)
-        else:  # more than four matrices or an odd K: compose on the device with torch
-            hit = torch.cat(list(ws), dim=0)
-            if gamma is not None:
-                hit = (hit.float() * gamma.float()[None, :]).to(hit.dtype)
-            hit = hit.contiguous()
-        _prepared[k] = hit
-    return hit
+            return ops.prepare_weight(ws, gamma)
+        # more than four matrices or an odd K: compose on the device with torch
+        hit = torch.cat(list(ws), dim=0)
+        if gamma is not None:
+            hit = (hit.float() * gamma.float()[None, :]).to(hit.dtype)
+        return hit.contiguous()
+
+    sources = ws if gamma is None else ws + (gamma,)
+    return _prepared.get(sources, build)
 
 
 @torch.fx.wrap
@@ -106,6 +153,19 @@ def hb_rms_rowstat(x, eps):
 def hb_softmax(x, scale=1.0):
     """softmax(scale * x) over the last dimension in one kernel (``hb_row_softmax``)."""
     return ops.row_softmax(x, scale)
+
+
+@torch.fx.wrap
+def hb_matmul(a, b):
+    """``torch.matmul(a, b)`` for 16-bit operands on the tcgen05 GEMM: a 2-D ``b`` is one product
+    (``_tilelang_gemm_wrapper``), equal leading dimensions are a batch (``_tilelang_bmm_wrapper``, one
+    launch with the batch in the tile list).  The right operand is read where it lies, row-major
+    [K, N] or a transposed view of [N, K] storage."""
+    if b.dim() == 2:
+        return ops.gemm(a, b)
+    lead = a.shape[:-2]
+    out = ops.bmm(a.reshape(-1, a.shape[-2], a.shape[-1]), b.reshape(-1, b.shape[-2], b.shape[-1]))
+    return out.reshape(*lead, a.shape[-2], b.shape[-1])
 
 
 GEMM_LEAVES = (hb_linear, hb_swiglu, hb_linear_multi)
@@ -277,7 +337,9 @@ def _pass_residual(gm: fx.GraphModule) -> int:
     """add(r, gemm_leaf(...)) with the leaf used once -> residual=r inside the epilogue."""
     n = 0
     for node in list(gm.graph.nodes):
-        if _fname(node) not in ("add", "iadd") or len(node.args) != 2 or node.kwargs:
+        # functional adds only: an in-place add that survived canonicalisation mutates storage the
+        # caller can see, which a fresh output tensor would not reproduce
+        if _fname(node) != "add" or len(node.args) != 2 or node.kwargs:
             continue
         for r, g in (node.args, node.args[::-1]):
             if not (isinstance(r, fx.Node) and isinstance(g, fx.Node)):
@@ -286,8 +348,8 @@ def _pass_residual(gm: fx.GraphModule) -> int:
                 continue
             if _meta_shape(r) is not None and _meta_shape(r) != _meta_shape(node):
                 continue  # broadcasting add
-            if r in g.all_input_nodes and False:
-                continue
+            if _meta_dtype(r) is not None and _meta_dtype(g) is not None and _meta_dtype(r) != _meta_dtype(g):
+                continue  # eager would promote (e.g. an fp32 residual stream): keep its add
             kwargs = dict(g.kwargs)
             kwargs["residual"] = r
             # the leaf must come after r in the graph: re-create it at the add's position
@@ -449,6 +511,10 @@ def _pass_merge_siblings(gm: fx.GraphModule) -> int:
             widths.append(None if ws is None else ws[0])
         if any(w is None for w in widths):
             continue
+        if len({_meta_dtype(n.args[1]) for n in order}) != 1:
+            continue  # mixed weight dtypes cannot share one stacked operand
+        if rot and any(w % rot[0].kwargs["head_dim"] for w in widths):
+            continue  # the rotary epilogue works on whole head_dim-wide column groups
         order_in_graph = {n: i for i, n in enumerate(gm.graph.nodes)}
         last = max(nodes, key=lambda n: order_in_graph[n])
         kwargs = {"row_scale": row_scale, "gamma": gamma}
@@ -472,6 +538,40 @@ def _pass_merge_siblings(gm: fx.GraphModule) -> int:
         legalize_graph(gm)
         gm.graph.eliminate_dead_code()
     return merged
+
+
+def _pass_matmul(gm: fx.GraphModule) -> int:
+    """matmul / bmm / mm / ``@`` of 16-bit tensors that is not an nn.Linear call (attention the
+    rewrites refused, hand-written projections) -> ``hb_matmul``.  The reference has per-op leaves
+    for these (backend.py:258-272, 523-536) whose rewriters are disabled (:1487-1491)."""
+    done = 0
+    for n in list(gm.graph.nodes):
+        if n.op == "call_function" and (_fname(n) in ("matmul", "bmm", "mm") or n.target is operator.matmul):
+            pass
+        elif n.op == "call_method" and _fname(n) in ("matmul", "bmm", "mm"):
+            pass
+        else:
+            continue
+        if len(n.args) != 2 or n.kwargs:
+            continue
+        a, b = n.args
+        sa, sb = _meta_shape(a), _meta_shape(b)
+        if sa is None or sb is None or _meta_dtype(a) not in (torch.bfloat16, torch.float16) \
+                or _meta_dtype(b) != _meta_dtype(a):
+            continue
+        if len(sa) < 2 or len(sb) < 2 or sa[-1] != sb[-2] or sa[-1] % 8 or sb[-1] % 8:
+            continue
+        if len(sb) > 2 and tuple(sa[:-2]) != tuple(sb[:-2]):
+            continue  # broadcast batch dimensions stay in PyTorch
+        with gm.graph.inserting_before(n):
+            new = gm.graph.call_function(hb_matmul, (a, b))
+        new.meta = dict(n.meta)
+        n.replace_all_uses_with(new)
+        gm.graph.erase_node(n)
+        done += 1
+    if done:
+        gm.graph.eliminate_dead_code()
+    return done
 
 
 def _softmax_dim(n: fx.Node):
@@ -535,6 +635,7 @@ def fuse_gemm_epilogues(gm: fx.GraphModule) -> int:
     _pass_fold_rmsnorm(gm)
     _pass_rope(gm)
     _pass_merge_siblings(gm)
+    _pass_matmul(gm)
     _pass_softmax(gm)
     gm.graph.lint()
     gm.recompile()

@@ -286,6 +286,76 @@ def gemm_epilogue(a: torch.Tensor, w: torch.Tensor, epilogue: str = "none", *,
     return out2.reshape(*lead, n_out) if out is None else out
 
 
+def _mult8(*values: int) -> bool:
+    return all(int(v) % 8 == 0 for v in values)
+
+
+def bmm(a: torch.Tensor, b: torch.Tensor, epilogue: str = "none", *, bias: Optional[torch.Tensor] = None,
+        residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``epilogue(a @ b)`` for a [B, M, K] and b [B, K, N] (``torch.bmm``) in one launch of the tcgen05 GEMM:
+    the batch index is part of the tile list.  ``b`` is read where it lies — row-major [K, N] slices through
+    the MN-major operand path, ``w.transpose(-1, -2)`` views of [N, K] storage through the K-major one — so
+    neither layout is copied.  Replaces the reference's batched kernel
+    (Heddle/heddle/frontend/backend.py:491-536).  K, N and the strides must be multiples of 8 elements."""
+    _require_cuda(a, b, bias, residual)
+    if a.dim() != 3 or b.dim() != 3 or a.shape[0] != b.shape[0] or a.shape[2] != b.shape[1]:
+        raise ValueError(f"bmm needs [B, M, K] x [B, K, N], got {tuple(a.shape)} and {tuple(b.shape)}")
+    if a.dtype not in (torch.bfloat16, torch.float16) or b.dtype != a.dtype:
+        raise TypeError(f"bmm needs matching bf16/fp16 operands, got {a.dtype} and {b.dtype}")
+    if epilogue not in ("none", "silu", "relu", "gelu_tanh", "sigmoid", "tanh"):
+        raise ValueError(f"bmm takes the unary epilogues only, not {epilogue!r}")
+    Bn, M, K = a.shape
+    N = b.shape[2]
+    if not _mult8(K, N):
+        raise ValueError(f"bmm needs K and N to be multiples of 8 (K={K}, N={N})")
+    if a.stride(2) != 1 or not _mult8(a.stride(1), a.stride(0)) or a.data_ptr() % 16:
+        a = a.contiguous()
+    if b.stride(1) == 1 and b.stride(2) >= K and _mult8(b.stride(2), b.stride(0)) and b.data_ptr() % 16 == 0 and K > 1:
+        layout, ldw = _lib.HB_W_NK, b.stride(2)   # a transposed view of [B, N, K] storage
+    else:
+        if b.stride(2) != 1 or not _mult8(b.stride(1), b.stride(0)) or b.data_ptr() % 16:
+            b = b.contiguous()
+        layout, ldw = _lib.HB_W_KN, b.stride(1)
+    out = torch.empty((Bn, M, N), dtype=a.dtype, device=a.device)
+    if Bn == 0 or M == 0:
+        return out
+    g = _lib.GemmArgs()
+    g.a, g.w, g.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldw, g.ldo = a.stride(1), ldw, N
+    g.dtype = _DTYPES[a.dtype]
+    g.epilogue = _lib.EPILOGUES[epilogue]
+    g.batch, g.w_layout = Bn, layout
+    g.a_batch_stride, g.w_batch_stride, g.o_batch_stride = a.stride(0), b.stride(0), M * N
+    keep = []
+    if bias is not None:
+        bb = bias.to(a.dtype).contiguous()
+        if bb.numel() != N:
+            raise ValueError("bias must have N entries")
+        keep.append(bb)
+        g.bias = bb.data_ptr()
+    if residual is not None:
+        r = residual.to(a.dtype).expand(Bn, M, N).contiguous()
+        keep.append(r)
+        g.residual, g.ldr, g.r_batch_stride = r.data_ptr(), N, M * N
+    g.stream = _stream_ptr(a.device)
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.load().hb_gemm_epilogue(C.byref(g)))
+    return out
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, epilogue: str = "none", *, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``epilogue(a @ b)`` for a (..., K) and b [K, N] (``torch.mm`` / ``matmul`` with a 2-D right operand);
+    the counterpart of the reference's plain GEMM (Heddle/heddle/frontend/backend.py:227-272)."""
+    if b.dim() != 2 or a.shape[-1] != b.shape[0]:
+        raise ValueError(f"gemm needs (..., K) x [K, N], got {tuple(a.shape)} and {tuple(b.shape)}")
+    lead = a.shape[:-1]
+    r = None if residual is None else residual.reshape(1, -1, b.shape[1])
+    out = bmm(a.reshape(1, -1, a.shape[-1]), b.unsqueeze(0), epilogue, bias=bias, residual=r)
+    return out.reshape(*lead, b.shape[1])
+
+
 def rms_rowstat(x: torch.Tensor, residual: Optional[torch.Tensor] = None, eps: float = 1e-5,
                 write_sum: bool = False) -> "Tuple[Optional[torch.Tensor], torch.Tensor]":
     """Row statistic of RMSNorm fused with the residual add (``hb_rms_rowstat``).

@@ -184,6 +184,8 @@ typedef enum hb_epilogue {
   HB_EPI_ROPE = 7
 } hb_epilogue;
 
+typedef enum hb_w_layout { HB_W_NK = 0, HB_W_KN = 1 } hb_w_layout;
+
 typedef struct hb_gemm_args {
   const void* a; /* [M, K], row stride lda */
   const void* w; /* [N, K], row stride ldw */
@@ -201,6 +203,16 @@ typedef struct hb_gemm_args {
   int32_t rope_seq, head_dim;
   int32_t rope_cols;       /* ROPE: columns [0, rope_cols) are rotated, the rest copied */
   void* stream;
+  /* Batched products and the [K, N] operand layout (zero-initialised fields = one product, w [N, K]).
+   * batch > 1: out[b] = epilogue(a[b] . w[b]) for b < batch, replacing the reference's batched kernel
+   * (Heddle/heddle/frontend/backend.py:491-536, _build_bmm_kernel / _tilelang_bmm_wrapper); the batch
+   * strides are in elements, 0 = densely packed; row_scale is [batch * M], bias [N] is shared.
+   * w_layout HB_W_KN: w is [K, N] row-major with row stride ldw, as torch.mm / torch.bmm and the
+   * reference's plain GEMM take it (backend.py:227-272, _build_gemm_kernel / _tilelang_gemm_wrapper);
+   * plain epilogues only. */
+  int32_t batch;
+  int32_t w_layout;
+  int64_t a_batch_stride, w_batch_stride, o_batch_stride, r_batch_stride;
 } hb_gemm_args;
 
 int hb_gemm_epilogue(const hb_gemm_args* args);

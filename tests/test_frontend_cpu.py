@@ -32,7 +32,7 @@ def targets(gm):
     return [n.target for n in gm.graph.nodes if n.op == "call_function"]
 
 
-def qkv(B_=1, H=2, S=64, D=64, Skv=None, dtype=torch.float32):
+def qkv(B_=1, H=2, S=64, D=64, Skv=None, dtype=torch.bfloat16):
     g = torch.Generator().manual_seed(0)
     Skv = Skv or S
     return (torch.randn(B_, H, S, D, generator=g).to(dtype), torch.randn(B_, H, Skv, D, generator=g).to(dtype),
@@ -73,7 +73,7 @@ def test_sdpa_with_mask_or_dropout_is_left_alone():
             return F.scaled_dot_product_attention(q, k, v, attn_mask=m)
 
     q, k, v = qkv()
-    gm = capture(M(), q, k, v, torch.zeros(64, 64))
+    gm = capture(M(), q, k, v, torch.zeros(64, 64, dtype=q.dtype))
     assert B._tilelang_sdpa_direct not in targets(gm)
 
 
@@ -96,7 +96,7 @@ def test_expanded_attention_with_causal_mask_and_past():
         def forward(self, q, k, v):
             s = torch.matmul(q, k.transpose(-2, -1)) * 0.125
             Sq, Skv = q.shape[-2], k.shape[-2]
-            s = s + torch.triu(torch.full((Sq, Skv), float("-inf")), diagonal=Skv - Sq + 1)
+            s = s + torch.triu(torch.full((Sq, Skv), float("-inf"), dtype=q.dtype), diagonal=Skv - Sq + 1)
             return torch.matmul(torch.softmax(s, dim=-1), v)
 
     gm = capture(Attn(), *qkv(1, 2, 48, 64, Skv=80))
@@ -112,13 +112,13 @@ def test_expanded_attention_with_other_mask_is_left_alone():
             return torch.matmul(torch.softmax(s, dim=-1), v)
 
     q, k, v = qkv()
-    gm = capture(Attn(), q, k, v, torch.randn(64, 64))
+    gm = capture(Attn(), q, k, v, torch.randn(64, 64).to(q.dtype))
     assert B._tilelang_sdpa_direct not in targets(gm)
     # a mask that is triangular but not the causal one for these lengths
     class Attn2(torch.nn.Module):
         def forward(self, q, k, v):
             s = torch.matmul(q, k.transpose(-2, -1)) * 0.125
-            s = s + torch.triu(torch.full((64, 64), float("-inf")), diagonal=3)
+            s = s + torch.triu(torch.full((64, 64), float("-inf"), dtype=q.dtype), diagonal=3)
             return torch.matmul(torch.softmax(s, dim=-1), v)
 
     assert B._tilelang_sdpa_direct not in targets(capture(Attn2(), q, k, v))
@@ -130,7 +130,7 @@ def test_bshd_pattern_uses_the_bshd_wrapper():
             return patterns.scaled_dot_product_attention_pattern(q, k, v, 0.125)
 
     g = torch.Generator().manual_seed(0)
-    q, k, v = (torch.randn(2, 32, 4, 64, generator=g) for _ in range(3))
+    q, k, v = (torch.randn(2, 32, 4, 64, generator=g).to(torch.bfloat16) for _ in range(3))
     gm = capture(M(), q, k, v)
     assert patterns.tilelang_flash_attn_wrapper in targets(gm)
     assert not any("softmax" in str(t) for t in targets(gm))
@@ -140,7 +140,7 @@ def test_h2o_structure_is_fused_with_both_outputs():
     class H2O(torch.nn.Module):
         def forward(self, q, k, v):
             s = torch.matmul(q, k.transpose(-2, -1)) / 8.0
-            s = s + torch.triu(torch.full((64, 64), float("-inf")), diagonal=1)
+            s = s + torch.triu(torch.full((64, 64), float("-inf"), dtype=q.dtype), diagonal=1)
             p = torch.softmax(s, dim=-1)
             return torch.matmul(p, v), p.sum(dim=-2)
 
@@ -149,6 +149,101 @@ def test_h2o_structure_is_fused_with_both_outputs():
     assert B._tilelang_h2o_attention in t and B._tilelang_sdpa_direct not in t
     node = next(n for n in gm.graph.nodes if n.target is B._tilelang_h2o_attention)
     assert node.kwargs == {"is_causal": True, "scale": pytest.approx(0.125)}
+
+
+def test_operands_the_kernels_cannot_take_stay_eager():
+    """The rewrites are decided from the captured shapes and dtypes: what the sm_100a kernels cannot
+    compute exactly as eager does stays an eager node instead of failing (or differing) at run time."""
+    class Sdpa(torch.nn.Module):
+        def __init__(self, causal):
+            super().__init__()
+            self.causal = causal
+
+        def forward(self, q, k, v):
+            return F.scaled_dot_product_attention(q, k, v, is_causal=self.causal)
+
+    # is_causal=True with Sq != Skv: eager masks from the top-left corner, the kernel from the end of the keys
+    assert B._tilelang_sdpa_direct not in targets(capture(Sdpa(True), *qkv(1, 2, 48, 64, Skv=80)))
+    assert B._tilelang_sdpa_direct in targets(capture(Sdpa(False), *qkv(1, 2, 48, 64, Skv=80)))
+    assert B._tilelang_sdpa_direct in targets(capture(Sdpa(True), *qkv(1, 2, 64, 64)))
+    # head_dim 96, fp32 operands, 3-D operands
+    assert B._tilelang_sdpa_direct not in targets(capture(Sdpa(False), *qkv(1, 2, 64, 96)))
+    assert B._tilelang_sdpa_direct not in targets(capture(Sdpa(False), *qkv(1, 2, 64, 64, dtype=torch.float32)))
+    q, k, v = qkv(1, 2, 64, 64)
+    assert B._tilelang_sdpa_direct not in targets(capture(Sdpa(False), q[0], k[0], v[0]))
+
+    class Expanded(torch.nn.Module):
+        def forward(self, q, k, v):
+            s = torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(q.shape[-1])
+            return torch.matmul(torch.softmax(s, dim=-1), v)
+
+    assert B._tilelang_sdpa_direct not in targets(capture(Expanded(), *qkv(1, 2, 64, 64, dtype=torch.float32)))
+    assert B._tilelang_sdpa_direct not in targets(capture(Expanded(), *qkv(1, 2, 64, 80)))
+    g = torch.Generator().manual_seed(0)
+    bshd = [torch.randn(2, 32, 4, 64, generator=g) for _ in range(3)]  # fp32
+
+    class Bshd(torch.nn.Module):
+        def forward(self, q, k, v):
+            return patterns.scaled_dot_product_attention_pattern(q, k, v, 0.125)
+
+    assert patterns.tilelang_flash_attn_wrapper not in targets(capture(Bshd(), *bshd))
+
+
+def test_inplace_and_hand_written_softmax_spellings_still_match():
+    """canonicalize_ops / recompose_softmax run in front of the matchers (the reference runs
+    canonicalize_ops and decompose_ops in front of its partitioner, backend.py:1521-1530)."""
+    class InplaceScale(torch.nn.Module):
+        def forward(self, q, k, v):
+            s = torch.matmul(q, k.transpose(-2, -1))
+            s *= 0.125
+            s += torch.triu(torch.full((64, 64), float("-inf"), dtype=q.dtype), diagonal=1)
+            return torch.matmul(torch.softmax(s, dim=-1), v)
+
+    gm = capture(InplaceScale(), *qkv())
+    nodes = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is B._tilelang_sdpa_direct]
+    assert len(nodes) == 1 and nodes[0].kwargs == {"is_causal": True, "scale": 0.125}
+
+    class SafeSoftmaxByHand(torch.nn.Module):
+        def forward(self, q, k, v):
+            s = torch.matmul(q, k.transpose(-2, -1)) / 8.0
+            e = torch.exp(s - torch.amax(s, dim=-1, keepdim=True))
+            p = e / torch.sum(e, dim=-1, keepdim=True)
+            return torch.matmul(p, v)
+
+    gm = capture(SafeSoftmaxByHand(), *qkv())
+    assert targets(gm) == [B._tilelang_sdpa_direct]
+
+    class ResidualInPlace(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(64, 64, bias=False)
+            self.b = torch.nn.Linear(64, 64, bias=False)
+
+        def forward(self, x):
+            h = F.silu(self.a(x))
+            h = h.clone()
+            y = self.b(h)
+            y += h            # h is produced inside the graph: the in-place add is unobservable
+            return y
+
+    gm = capture(ResidualInPlace().to(torch.bfloat16), torch.randn(4, 16, 64).to(torch.bfloat16))
+    lin = [n for n in gm.graph.nodes if n.target is fusion.hb_linear]
+    assert len(lin) == 2 and lin[1].kwargs.get("residual") is lin[0]
+    assert not any(getattr(t, "__name__", "") in ("iadd", "clone") for t in targets(gm))
+
+    class MutatesItsInput(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(64, 64, bias=False)
+
+        def forward(self, x):
+            x += self.a(x)    # the caller sees x change: must stay an in-place add on x
+            return x
+
+    gm = capture(MutatesItsInput().to(torch.bfloat16), torch.randn(4, 16, 64).to(torch.bfloat16))
+    lin = [n for n in gm.graph.nodes if n.target is fusion.hb_linear]
+    assert len(lin) == 1 and lin[0].kwargs.get("residual") is None
+    assert any(getattr(t, "__name__", "") == "iadd" for t in targets(gm))
 
 
 def test_env_switch_disables_attention_rewrite(monkeypatch):

@@ -174,3 +174,76 @@ def test_row_softmax(ops, rows, cols, dtype):
     assert (y3.float().cpu() - torch.softmax(x3.float(), -1)).abs().max().item() <= 4e-3
     with pytest.raises(RuntimeError, match="multiple of 8"):
         ops.row_softmax(torch.zeros(4, 12, dtype=dtype, device="cuda"))
+
+
+# ----------------------------------------------------------------------------------------
+# batched products and the [K, N] operand layout
+# ----------------------------------------------------------------------------------------
+def _bmm_ref(a, b, act="none"):
+    return O.epilogue_fp32(torch.matmul(a.float(), b.float()), act)
+
+
+@pytest.mark.parametrize("Bn,M,N,K", [(1, 128, 256, 64), (3, 200, 136, 72), (8, 64, 64, 64), (5, 300, 520, 256),
+                                      (16, 1024, 128, 1024), (2, 8, 8, 8)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_bmm_row_major_operands(ops, Bn, M, N, K, dtype):
+    g = torch.Generator().manual_seed(Bn * 7 + M + N + K)
+    a = torch.randn(Bn, M, K, generator=g).to(dtype)
+    b = (torch.randn(Bn, K, N, generator=g) * 0.05).to(dtype)
+    out = ops.bmm(a.cuda(), b.cuda())
+    torch.cuda.synchronize()
+    assert ops.status_word() == 0
+    _close(out, _bmm_ref(a, b), tol=1e-2)
+
+
+def test_bmm_transposed_view_and_strided_batches(ops):
+    g = torch.Generator().manual_seed(11)
+    a = torch.randn(4, 96, 128, generator=g).to(torch.bfloat16)
+    w = (torch.randn(4, 200, 128, generator=g) * 0.05).to(torch.bfloat16)       # [B, N, K] storage
+    out = ops.bmm(a.cuda(), w.cuda().transpose(1, 2))                            # read K-major, no copy
+    _close(out, _bmm_ref(a, w.transpose(1, 2)), tol=1e-2)
+    # batches that are slices of a larger tensor (batch stride larger than one matrix)
+    big = torch.randn(4, 2, 96, 128, generator=g).to(torch.bfloat16)
+    bk = (torch.randn(4, 2, 128, 72, generator=g) * 0.05).to(torch.bfloat16)
+    out = ops.bmm(big.cuda()[:, 1], bk.cuda()[:, 0], "gelu_tanh")
+    _close(out, _bmm_ref(big[:, 1], bk[:, 0], "gelu_tanh"), tol=1e-2)
+
+
+def test_gemm_with_kn_operand_bias_and_residual(ops):
+    g = torch.Generator().manual_seed(12)
+    a = torch.randn(3, 50, 264, generator=g).to(torch.float16)
+    b = (torch.randn(264, 328, generator=g) * 0.05).to(torch.float16)
+    bias = torch.randn(328, generator=g).to(torch.float16)
+    res = torch.randn(3, 50, 328, generator=g).to(torch.float16)
+    out = ops.gemm(a.cuda(), b.cuda(), "silu", bias=bias.cuda(), residual=res.cuda())
+    ref = O.epilogue_fp32(torch.matmul(a.float(), b.float()) + bias.float(), "silu") + res.float()
+    _close(out, ref, tol=1e-2)
+
+
+def test_reference_named_gemm_leaves(ops):
+    """The per-op leaves of Heddle/heddle/frontend/backend.py:258-300, 523-536, 572-598 by name."""
+    from heddle_b200.frontend import backend as Bk
+
+    g = torch.Generator().manual_seed(13)
+    a = torch.randn(160, 128, generator=g).to(torch.bfloat16)
+    b = (torch.randn(128, 192, generator=g) * 0.05).to(torch.bfloat16)
+    _close(Bk._tilelang_gemm_wrapper(a.cuda(), b.cuda()), _bmm_ref(a, b), tol=1e-2)
+    x = torch.randn(2, 80, 128, generator=g).to(torch.bfloat16)
+    w = (torch.randn(192, 128, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(192, 128, generator=g) * 0.05).to(torch.bfloat16)
+    x2 = x.reshape(-1, 128)
+    _close(Bk._tilelang_linear_wrapper(x.cuda(), w.cuda()), O.gemm_epilogue(x2, w, "none").reshape(2, 80, 192), tol=1e-2)
+    _close(Bk._tilelang_swiglu_wrapper(x.cuda(), w.cuda(), w2.cuda()),
+           O.gemm_epilogue(x2, torch.cat([w, w2]), "swiglu").reshape(2, 80, 192), tol=1e-2)
+    a3 = torch.randn(4, 96, 64, generator=g).to(torch.bfloat16)
+    b3 = (torch.randn(4, 64, 72, generator=g) * 0.05).to(torch.bfloat16)
+    _close(Bk._tilelang_bmm_wrapper(a3.cuda(), b3.cuda()), _bmm_ref(a3, b3), tol=1e-2)
+
+
+def test_bmm_rejects_what_it_cannot_take(ops):
+    a = torch.zeros(2, 16, 12, dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros(2, 12, 16, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="multiples of 8"):
+        ops.bmm(a, b)
+    with pytest.raises(TypeError):
+        ops.bmm(a.float(), b.float())
