@@ -107,9 +107,36 @@ class PrepareArgs(C.Structure):
     ]
 
 
+EW_OPS = {
+    "load": 0, "add": 1, "sub": 2, "rsub": 3, "mul": 4, "div": 5, "rdiv": 6, "max": 7, "min": 8, "pow": 9,
+    "neg": 16, "abs": 17, "exp": 18, "log": 19, "log2": 20, "sqrt": 21, "rsqrt": 22, "recip": 23, "sigmoid": 24,
+    "silu": 25, "relu": 26, "gelu_tanh": 27, "gelu_erf": 28, "tanh": 29, "round": 30, "store_tmp": 40,
+    "reduce_sum": 48, "reduce_max": 49, "reduce_mean": 50, "store_out": 56,
+}
+EW_SRCS = {"none": 0, "input": 1, "imm": 2, "tmp": 3, "rowvec": 4, "rowscalar": 5, "reduced": 6}
+EW_MAX_INST, EW_MAX_INPUTS, EW_MAX_ROWVEC, EW_MAX_ROWSCALAR, EW_MAX_OUTPUTS, EW_MAX_TMP, EW_MAX_RED = 48, 6, 4, 4, 2, 4, 4
+
+
+class EwInst(C.Structure):
+    """Mirror of hb_ew_inst."""
+    _fields_ = [("op", C.c_int32), ("src", C.c_int32), ("index", C.c_int32), ("imm", C.c_float)]
+
+
+class RowwiseArgs(C.Structure):
+    """Mirror of hb_rowwise_args."""
+    _fields_ = [
+        ("inputs", C.c_void_p * EW_MAX_INPUTS), ("ld_in", C.c_int64 * EW_MAX_INPUTS),
+        ("rowvec", C.c_void_p * EW_MAX_ROWVEC), ("rowscalar", C.c_void_p * EW_MAX_ROWSCALAR),
+        ("outputs", C.c_void_p * EW_MAX_OUTPUTS), ("ld_out", C.c_int64 * EW_MAX_OUTPUTS),
+        ("n_inputs", C.c_int32), ("n_rowvec", C.c_int32), ("n_rowscalar", C.c_int32), ("n_outputs", C.c_int32),
+        ("rows", C.c_int64), ("cols", C.c_int32), ("dtype", C.c_int32), ("n_inst", C.c_int32),
+        ("program", EwInst * EW_MAX_INST), ("stream", C.c_void_p),
+    ]
+
+
 # every symbol include/heddle_b200.h declares
 EXPORTS = (
-    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_status_word_noalloc", "hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_status_word",
+    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_status_word_noalloc", "hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_rowwise_program", "hb_status_word",
     "hb_version",
     "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma", "hb_debug_wait_timeout",
 )
@@ -147,6 +174,8 @@ def load() -> C.CDLL:
     lib.hb_row_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_float,
                                    C.c_int32, C.c_void_p]
     lib.hb_row_softmax.restype = C.c_int
+    lib.hb_rowwise_program.argtypes = [C.POINTER(RowwiseArgs)]
+    lib.hb_rowwise_program.restype = C.c_int
     lib.hb_status_word.argtypes = [C.POINTER(C.c_uint32)]
     lib.hb_status_word.restype = C.c_int
     lib.hb_status_word_noalloc.argtypes = [C.POINTER(C.c_uint32), C.c_void_p]

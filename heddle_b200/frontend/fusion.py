@@ -168,6 +168,13 @@ def hb_matmul(a, b):
     return out.reshape(*lead, a.shape[-2], b.shape[-1])
 
 
+@torch.fx.wrap
+def hb_rowwise(inputs, rowvecs, rowscalars, program, n_outputs=1):
+    """A fused group of pointwise / row-reduction nodes as one ``hb_rowwise_program`` launch.
+    ``program`` is the accumulator-machine program ``partitioner.lower_partition`` produced."""
+    return ops.rowwise_program(program, inputs, rowvecs, rowscalars, n_outputs)
+
+
 GEMM_LEAVES = (hb_linear, hb_swiglu, hb_linear_multi)
 
 
@@ -626,6 +633,44 @@ def _pass_softmax(gm: fx.GraphModule) -> int:
     return done
 
 
+def _pass_rowwise(gm: fx.GraphModule) -> int:
+    """What is left of the graph's pointwise chains and last-axis reductions -> ``hb_rowwise`` leaves:
+    SupportPolicy decides membership, GraphPartitioner groups and prunes
+    (TILELANG_FRONTEND_MIN_NODES / MIN_ELEMS / MIN_AI), lower_partition writes the program.  The
+    reference sends the same partitions through its elementwise / reduction code generators
+    (backend.py:1603-1700, codegen.py:1246-1498)."""
+    from .partitioner import GraphPartitioner, lower_partition
+
+    gp = GraphPartitioner(gm)
+    done = 0
+    for part in gp.partition():
+        lp = lower_partition(part, gp.support)
+        if lp is None:
+            continue
+        last = part.nodes[-1]
+        with gm.graph.inserting_after(last):
+            leaf = gm.graph.call_function(hb_rowwise, (list(lp.inputs), list(lp.rowvecs), list(lp.rowscalars),
+                                                        lp.program, len(lp.outputs)))
+        if len(lp.outputs) == 1:
+            leaf.meta = dict(lp.outputs[0].meta)
+            lp.outputs[0].replace_all_uses_with(leaf)
+        else:
+            prev = leaf
+            for i, o in enumerate(lp.outputs):
+                with gm.graph.inserting_after(prev):
+                    item = gm.graph.call_function(operator.getitem, (leaf, i))
+                item.meta = dict(o.meta)
+                o.replace_all_uses_with(item)
+                prev = item
+        done += 1
+    if done:
+        from torch.fx.passes.tools_common import legalize_graph
+
+        legalize_graph(gm)
+        gm.graph.eliminate_dead_code()
+    return done
+
+
 def fuse_gemm_epilogues(gm: fx.GraphModule) -> int:
     """Run all passes; returns the number of GEMM leaves in the rewritten graph."""
     _pass_rmsnorm(gm)
@@ -637,6 +682,7 @@ def fuse_gemm_epilogues(gm: fx.GraphModule) -> int:
     _pass_merge_siblings(gm)
     _pass_matmul(gm)
     _pass_softmax(gm)
+    _pass_rowwise(gm)
     gm.graph.lint()
     gm.recompile()
     return sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target in GEMM_LEAVES)

@@ -429,6 +429,64 @@ def row_softmax(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     return y.reshape(x.shape)
 
 
+def rowwise_program(program, inputs=(), rowvecs=(), rowscalars=(), n_outputs: int = 1):
+    """Run an accumulator-machine program over [rows, cols] views of ``inputs`` (``hb_rowwise_program``).
+
+    ``program`` is a sequence of ``(op, src, index, imm)`` tuples with the names of ``_lib.EW_OPS`` /
+    ``_lib.EW_SRCS`` (``src`` may be None for unary ops).  ``inputs`` are 16-bit tensors of one shape
+    (..., cols); ``rowvecs`` are [cols] vectors; ``rowscalars`` are tensors with one value per row
+    (shape (..., 1) or (...)), converted to fp32.  Returns ``n_outputs`` new tensors shaped like the
+    inputs (a tuple when ``n_outputs`` > 1)."""
+    if not inputs:
+        raise ValueError("rowwise_program needs at least one full-size input")
+    _require_cuda(*inputs, *rowvecs, *rowscalars)
+    x0 = inputs[0]
+    if x0.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"rowwise_program takes bf16/fp16 tensors, got {x0.dtype}")
+    cols = x0.shape[-1]
+    shape = tuple(x0.shape)
+    a = _lib.RowwiseArgs()
+    keep = []
+    if len(inputs) > _lib.EW_MAX_INPUTS or len(rowvecs) > _lib.EW_MAX_ROWVEC or len(rowscalars) > _lib.EW_MAX_ROWSCALAR \
+            or not 1 <= n_outputs <= _lib.EW_MAX_OUTPUTS or not 1 <= len(program) <= _lib.EW_MAX_INST:
+        raise ValueError("rowwise_program: too many operands or instructions")
+    for i, t in enumerate(inputs):
+        if tuple(t.shape) != shape or t.dtype != x0.dtype:
+            raise ValueError("rowwise_program: full-size inputs must share shape and dtype")
+        t2 = t.reshape(-1, cols)
+        if t2.stride(-1) != 1 or t2.stride(0) % 8 or t2.data_ptr() % 16:
+            t2 = t2.contiguous()
+        keep.append(t2)
+        a.inputs[i], a.ld_in[i] = t2.data_ptr(), t2.stride(0)
+    rows = keep[0].shape[0]
+    for i, t in enumerate(rowvecs):
+        t2 = t.reshape(-1).to(x0.dtype).contiguous()
+        if t2.numel() != cols:
+            raise ValueError("rowwise_program: a row vector must have cols entries")
+        keep.append(t2)
+        a.rowvec[i] = t2.data_ptr()
+    for i, t in enumerate(rowscalars):
+        t2 = t.reshape(-1).to(torch.float32).contiguous()
+        if t2.numel() != rows:
+            raise ValueError("rowwise_program: a per-row vector must have one entry per row")
+        keep.append(t2)
+        a.rowscalar[i] = t2.data_ptr()
+    outs = [torch.empty(shape, dtype=x0.dtype, device=x0.device) for _ in range(n_outputs)]
+    for i, o in enumerate(outs):
+        a.outputs[i], a.ld_out[i] = o.data_ptr(), cols
+    a.n_inputs, a.n_rowvec, a.n_rowscalar, a.n_outputs = len(inputs), len(rowvecs), len(rowscalars), n_outputs
+    a.rows, a.cols, a.dtype, a.n_inst = rows, cols, _DTYPES[x0.dtype], len(program)
+    for pc, (op, src, index, imm) in enumerate(program):
+        a.program[pc].op = _lib.EW_OPS[op]
+        a.program[pc].src = _lib.EW_SRCS[src or "none"]
+        a.program[pc].index = int(index)
+        a.program[pc].imm = float(imm)
+    a.stream = _stream_ptr(x0.device)
+    with torch.cuda.device(x0.device):
+        _lib.check(_lib.load().hb_rowwise_program(C.byref(a)))
+    return outs[0] if n_outputs == 1 else tuple(outs)
+
+
 def h2o_score(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, *, causal: bool = True,
               softmax_scale: Optional[float] = None, layout: str = "bhsd") -> torch.Tensor:
     """H2O score through ``hb_h2o_score``: score[b,h,j] = sum_i exp(s_ij - lse_i), fp32 [B, Hq, Skv].

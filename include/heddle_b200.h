@@ -305,6 +305,102 @@ int hb_fa_bwd_dq(const hb_fa_bwd_args* args);
 int hb_row_softmax(const void* x, void* y, int64_t rows, int32_t cols, int64_t ld_x, int64_t ld_y,
                    float scale, int32_t dtype, void* stream);
 
+/*
+ * Pointwise chains and row reductions over a [rows, cols] matrix (bf16 / fp16 tensors, fp32 math),
+ * driven by an op-code program.  The native counterpart of the kernels the reference generates as
+ * source text and compiles at run time for its elementwise partitions
+ * (Heddle/heddle/frontend/codegen.py:1457-1498, op table _map_op :1577-1609) and for its
+ * softmax-like / sum / mean / max row reductions (:1246-1455: one pass per reduction that recomputes
+ * the expression up to it, reduction results kept in fp32, then an output pass).
+ *
+ * The program runs once per group of 8 consecutive columns of a row on an accumulator machine:
+ * `acc = op(acc, operand)`.  Operands: a full input tensor [rows, cols] (HB_SRC_INPUT), a [cols]
+ * vector of the same dtype broadcast over rows (HB_SRC_ROWVEC), an fp32 [rows] vector broadcast
+ * over columns (HB_SRC_ROWSCALAR), an immediate (HB_SRC_IMM), a saved value (HB_SRC_TMP, written
+ * by HB_EW_STORE_TMP) or the result of an earlier row reduction (HB_SRC_REDUCED).  Unary ops use
+ * no operand.  HB_EW_REDUCE_{SUM,MAX,MEAN} reduce acc over the whole row into slot `index` and leave
+ * acc unchanged; a program with R of them is run R + 1 times (prefix passes, then the whole
+ * program), so instructions in front of a reduction must not depend on that reduction.
+ * HB_EW_STORE_OUT writes acc, rounded to the dtype, to output `index`; HB_EW_ROUND rounds acc to
+ * the dtype and back (an intermediate 16-bit tensor of the eager graph).
+ * Constraints: cols a multiple of 8; pointers 16-byte aligned; row strides multiples of 8.
+ */
+typedef enum hb_ew_op {
+  HB_EW_LOAD = 0, /* acc = operand */
+  HB_EW_ADD = 1,
+  HB_EW_SUB = 2,  /* acc - operand */
+  HB_EW_RSUB = 3, /* operand - acc */
+  HB_EW_MUL = 4,
+  HB_EW_DIV = 5,  /* acc / operand */
+  HB_EW_RDIV = 6, /* operand / acc */
+  HB_EW_MAX = 7,
+  HB_EW_MIN = 8,
+  HB_EW_POW = 9,  /* acc ** operand */
+  HB_EW_NEG = 16,
+  HB_EW_ABS = 17,
+  HB_EW_EXP = 18,
+  HB_EW_LOG = 19,
+  HB_EW_LOG2 = 20,
+  HB_EW_SQRT = 21,
+  HB_EW_RSQRT = 22,
+  HB_EW_RECIP = 23,
+  HB_EW_SIGMOID = 24,   /* 1 / (1 + exp(-x)) */
+  HB_EW_SILU = 25,      /* x * sigmoid(x) */
+  HB_EW_RELU = 26,
+  HB_EW_GELU_TANH = 27, /* 0.5 x (1 + tanh(0.7978845608 (x + 0.044715 x^3))) */
+  HB_EW_GELU_ERF = 28,
+  HB_EW_TANH = 29,
+  HB_EW_ROUND = 30,
+  HB_EW_STORE_TMP = 40,
+  HB_EW_REDUCE_SUM = 48,
+  HB_EW_REDUCE_MAX = 49,
+  HB_EW_REDUCE_MEAN = 50,
+  HB_EW_STORE_OUT = 56
+} hb_ew_op;
+
+typedef enum hb_ew_src {
+  HB_SRC_NONE = 0,
+  HB_SRC_INPUT = 1,
+  HB_SRC_IMM = 2,
+  HB_SRC_TMP = 3,
+  HB_SRC_ROWVEC = 4,
+  HB_SRC_ROWSCALAR = 5,
+  HB_SRC_REDUCED = 6
+} hb_ew_src;
+
+#define HB_EW_MAX_INST 48
+#define HB_EW_MAX_INPUTS 6
+#define HB_EW_MAX_ROWVEC 4
+#define HB_EW_MAX_ROWSCALAR 4
+#define HB_EW_MAX_OUTPUTS 2
+#define HB_EW_MAX_TMP 4
+#define HB_EW_MAX_RED 4
+
+typedef struct hb_ew_inst {
+  int32_t op;    /* hb_ew_op */
+  int32_t src;   /* hb_ew_src */
+  int32_t index; /* operand / temporary / reduction slot / output index */
+  float imm;
+} hb_ew_inst;
+
+typedef struct hb_rowwise_args {
+  const void* inputs[HB_EW_MAX_INPUTS];
+  int64_t ld_in[HB_EW_MAX_INPUTS];
+  const void* rowvec[HB_EW_MAX_ROWVEC];
+  const float* rowscalar[HB_EW_MAX_ROWSCALAR];
+  void* outputs[HB_EW_MAX_OUTPUTS];
+  int64_t ld_out[HB_EW_MAX_OUTPUTS];
+  int32_t n_inputs, n_rowvec, n_rowscalar, n_outputs;
+  int64_t rows;
+  int32_t cols;
+  int32_t dtype; /* HB_BF16 or HB_FP16 */
+  int32_t n_inst;
+  hb_ew_inst program[HB_EW_MAX_INST];
+  void* stream;
+} hb_rowwise_args;
+
+int hb_rowwise_program(const hb_rowwise_args* args);
+
 /* Device-side status word of the current device (0 = no bounded wait ever gave up);
  * reading it synchronises the device.  *out always receives the word; the return value is
  * HB_OK when it is zero and HB_ERR_TIMEOUT otherwise (hb_last_error() then names the kernel

@@ -49,6 +49,9 @@ int main(void) {
          offsetof(hb_prepare_args, stream));
   printf("%zu %zu %zu %zu %zu\n", sizeof(hb_fa_bwd_args), offsetof(hb_fa_bwd_args, B), offsetof(hb_fa_bwd_args, q_stride_b),
          offsetof(hb_fa_bwd_args, causal), offsetof(hb_fa_bwd_args, stream));
+  printf("%zu %zu %zu\n", offsetof(hb_gemm_args, batch), offsetof(hb_gemm_args, w_layout), offsetof(hb_gemm_args, r_batch_stride));
+  printf("%zu %zu %zu %zu %zu %zu\n", sizeof(hb_rowwise_args), offsetof(hb_rowwise_args, rowscalar), offsetof(hb_rowwise_args, n_inputs),
+         offsetof(hb_rowwise_args, rows), offsetof(hb_rowwise_args, program), offsetof(hb_rowwise_args, stream));
   return 0;
 }'''
     with tempfile.TemporaryDirectory() as d:
@@ -70,6 +73,12 @@ int main(void) {
     bw = [int(x) for x in lines[4].split()]
     assert bw == [ctypes.sizeof(_lib.FaBwdArgs), _lib.FaBwdArgs.B.offset, _lib.FaBwdArgs.q_stride_b.offset,
                   _lib.FaBwdArgs.causal.offset, _lib.FaBwdArgs.stream.offset]
+    gb = [int(x) for x in lines[5].split()]
+    assert gb == [_lib.GemmArgs.batch.offset, _lib.GemmArgs.w_layout.offset, _lib.GemmArgs.r_batch_stride.offset]
+    rw = [int(x) for x in lines[6].split()]
+    assert rw == [ctypes.sizeof(_lib.RowwiseArgs), _lib.RowwiseArgs.rowscalar.offset, _lib.RowwiseArgs.n_inputs.offset,
+                  _lib.RowwiseArgs.rows.offset, _lib.RowwiseArgs.program.offset, _lib.RowwiseArgs.stream.offset]
+    assert ctypes.sizeof(_lib.EwInst) == 16
 
 
 def test_argument_validation_needs_no_gpu(built_lib):
@@ -115,6 +124,27 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert built_lib.hb_prepare_weight(ctypes.byref(w)) == _lib.HB_ERR_ALIGN  # K % 8
     w.K = 64
     assert built_lib.hb_prepare_weight(ctypes.byref(w)) == _lib.HB_ERR_BAD_ARG  # null output
+    # the rowwise program is checked on the host before anything is launched
+    assert built_lib.hb_rowwise_program(None) == _lib.HB_ERR_BAD_ARG
+    r = _lib.RowwiseArgs()
+    r.rows, r.cols, r.dtype, r.n_outputs, r.n_inst = 4, 60, _lib.HB_BF16, 1, 1
+    assert built_lib.hb_rowwise_program(ctypes.byref(r)) == _lib.HB_ERR_UNSUPPORTED  # cols % 8
+    r.cols = 64
+    assert built_lib.hb_rowwise_program(ctypes.byref(r)) == _lib.HB_ERR_ALIGN  # null output pointer
+    buf = (ctypes.c_uint8 * 4096)()
+    base = (ctypes.addressof(buf) + 15) & ~15
+    r.outputs[0], r.ld_out[0] = base, 64
+    r.program[0].op = _lib.EW_OPS["add"]
+    r.program[0].src = _lib.EW_SRCS["imm"]
+    assert built_lib.hb_rowwise_program(ctypes.byref(r)) == _lib.HB_ERR_BAD_ARG
+    assert b"before a LOAD" in built_lib.hb_last_error()
+    r.program[0].op = _lib.EW_OPS["load"]
+    assert built_lib.hb_rowwise_program(ctypes.byref(r)) == _lib.HB_ERR_BAD_ARG
+    assert b"never stored" in built_lib.hb_last_error()
+    r.n_inst = 2
+    r.program[1].op, r.program[1].src, r.program[1].index = _lib.EW_OPS["add"], _lib.EW_SRCS["tmp"], 1
+    assert built_lib.hb_rowwise_program(ctypes.byref(r)) == _lib.HB_ERR_BAD_ARG
+    assert b"before it is stored" in built_lib.hb_last_error()
 
 
 def test_ops_reject_cpu_tensors(built_lib):
