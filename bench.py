@@ -18,8 +18,14 @@ Printed by rank 0 as ONE JSON line:
   cpu_baseline  the CPU oracle (the reference's eager fp32 graph) on a bounded slice
   clocks     SM clock / throttle reasons sampled during the timed region
 
-``--impl reference`` times the reference's own CPU path for the same metric/config:
-its FX graph executed eagerly in fp32 by PyTorch on the host cores (the oracle port).
+  secondary  (N = 1) short runs of the other configurations: GQA (config 3, whole), FP8 (config 4), the fused
+             decoder layer (config 5), the plain projection GEMMs next to cuBLAS, H2O, the rowwise program
+  strong     (N > 1) the FIXED config-2 and config-3 problems split over the ranks by batch x KV head
+
+``--impl reference`` times the reference's own CPU path for the same metric/config: the attention
+module captured by the reference's ``tilelang_backend`` (from ``baseline/_ref``) with kernel generation
+off, i.e. its FX graph executed eagerly in fp32 on the host cores; when that package cannot be
+imported, the oracle port of the same graph.
 """
 from __future__ import annotations
 
@@ -40,6 +46,14 @@ import torch  # noqa: E402
 WORKLOAD = dict(B=4, H=32, S=4096, D=128, causal=True)
 METRIC = "attention_fwd_bf16_causal_tflops"
 UNIT = "TFLOP/s"
+
+
+def config_dict(world: int) -> dict:
+    """The workload description both arms print (identical for ``--impl ours`` and ``--impl reference``)."""
+    return {"workload": "bf16_causal_mha_B4_H32_S4096_D128", "global_batch": WORKLOAD["B"] * world,
+            "seq_len": WORKLOAD["S"], "heads": WORKLOAD["H"], "head_dim": WORKLOAD["D"], "causal": True,
+            "parallelism": f"dp{world}_batch_x_head_no_collective",
+            "l2": "inputs+outputs (268 MB per step) exceed the 126 MB L2; no explicit flush"}
 
 
 def algorithmic_flops(B, H, S, D, causal) -> float:
@@ -68,7 +82,7 @@ class ClockSampler:
         0x0000000000000080: "hw_power_brake_slowdown",
     }
 
-    def __init__(self, device_index: int, period_s: float = 0.005):
+    def __init__(self, device_index: int, period_s: float = 0.001):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
@@ -206,24 +220,88 @@ def reference_gpu_kernel(B, H, S, D, causal):
             sys.path.remove(str(ref_dir))
 
 
+class _EagerCausalAttention(torch.nn.Module):
+    """The attention of the workload written out as user code writes it; what the reference captures."""
+
+    def forward(self, q, k, v):
+        S = q.shape[-2]
+        s = torch.matmul(q, k.transpose(-2, -1)) / (q.shape[-1] ** 0.5)
+        s = s + torch.triu(torch.full((S, S), float("-inf")), diagonal=1)
+        return torch.matmul(torch.softmax(s, dim=-1), v)
+
+
+def _reference_cpu_callable():
+    """The reference's own CPU path: the module above compiled with the reference's torch.compile
+    backend (Heddle/heddle/frontend/backend.py:1421) from baseline/_ref, attention-kernel generation and
+    partition execution switched off, so that its decomposed FX graph runs eagerly in fp32.  Returns
+    (callable, kind) or (None, reason)."""
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "heddle").exists():
+        return None, "baseline/_ref/heddle not present"
+    import contextlib
+
+    os.environ["TILELANG_FRONTEND_ENABLE_FLASHATTN_PATTERN"] = "0"
+    os.environ["TILELANG_FRONTEND_ENABLE_H2O_FUSE"] = "0"
+    os.environ["TILELANG_FRONTEND_EXECUTE_PARTITIONS"] = "0"
+    os.environ.setdefault("TILELANG_DISABLE_CACHE", "1")
+    try:
+        sys.path.insert(0, str(ref_dir))
+        with contextlib.redirect_stdout(sys.stderr):  # the reference prints its graphs; stdout carries one JSON line
+            import heddle
+            heddle.init()
+            from heddle.frontend import tilelang_backend as reference_backend
+
+        torch._dynamo.reset()
+        compiled = torch.compile(_EagerCausalAttention(), backend=reference_backend)
+
+        def call(q, k, v):
+            with contextlib.redirect_stdout(sys.stderr), torch.no_grad():
+                out = compiled(q, k, v)
+            return out[0] if isinstance(out, (tuple, list)) else out
+
+        return call, "reference"
+    except Exception as e:  # noqa: BLE001
+        return None, f"{type(e).__name__}: {str(e)[:160]}"
+    finally:
+        if str(ref_dir) in sys.path:
+            sys.path.remove(str(ref_dir))
+
+
 def run_reference(args):
-    """Reference arm: the reference's CPU implementation of the path (its FX graph run
-    eagerly in fp32 = the oracle port), all host threads, bounded sample per step."""
+    """Reference arm: the reference's CPU implementation of the path on all host threads, a bounded
+    sample (a slice of the workload) per step.  Only rank 0 works."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     heads = 2
-    from oracle import attention_oracle as O
     use_all_host_threads()
     S, D = WORKLOAD["S"], WORKLOAD["D"]
-    q, k, v = O.make_qkv(1, heads, heads, S, S, D, seed=0, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(1, heads, S, D, generator=g).to(torch.bfloat16).float() for _ in range(3))
+    fn, kind = _reference_cpu_callable()
+    note = None
+    if fn is not None:
+        try:
+            fn(q, k, v)
+        except Exception as e:  # noqa: BLE001
+            fn, note = None, f"{type(e).__name__}: {str(e)[:160]}"
+    else:
+        note = kind
+    if fn is None:
+        from oracle import attention_oracle as O
+
+        kind = "port"
+
+        def fn(q, k, v):
+            return O.attention_eager(q, k, v, causal=True)[0]
+
     steps = max(1, min(args.steps, 20))
     warm = max(1, min(args.warmup, 2))
     for _ in range(warm):
-        O.attention_eager(q, k, v, causal=True)
+        fn(q, k, v)
     t0 = time.perf_counter()
     for _ in range(steps):
-        O.attention_eager(q, k, v, causal=True)
+        fn(q, k, v)
     dt = (time.perf_counter() - t0) / steps
     val = algorithmic_flops(1, heads, S, D, True) / dt / 1e12
     sample = f"each step = B=1 x {heads} heads x S={S} D={D} causal slice of the workload (1/{4 * 32 // heads} of it)"
@@ -231,13 +309,105 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "bf16_causal_mha_B4_H32_S4096_D128", "global_batch": WORKLOAD["B"] * args.gpus,
-                   "seq_len": S, "heads": WORKLOAD["H"], "head_dim": D, "causal": True, "parallelism": "cpu"},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "config": config_dict(args.gpus),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind, "sample": sample,
+                         "how": ("the attention module captured by the reference's tilelang_backend (baseline/_ref), kernel "
+                                 "generation off: its FX graph run eagerly in fp32" if kind == "reference" else
+                                 "oracle port of the reference's eager fp32 graph" + (f" (reference package unusable: {note})" if note else ""))},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------
+# secondary configurations and the fixed-problem split
+# ----------------------------------------------------------------------------------------
+def run_secondary(peaks) -> dict:
+    """Short device-resident runs (at most 20 launches each) of the configurations the headline does not
+    cover, each with its time, throughput, fraction of the stated peak and a tolerance check of sampled
+    heads against fp32 eager attention computed on the same GPU (TF32 off)."""
+    from heddle_b200 import bench_configs
+
+    out = {}
+    plan = [("c3", True), ("c4", True), ("c5", True), ("gemm", False), ("gemm_plain", False), ("bmm", False),
+            ("h2o", False), ("rowprog", False)]
+    for name, check in plan:
+        try:
+            r = bench_configs.run_config(name, steps=10 if name in ("c3", "c5", "gemm_plain") else 20, warmup=3, check=check)
+            if r.get("unit") == "TFLOP/s":
+                if name == "c4" and r.get("fp8_gemm_reference_tflops"):
+                    r["frac"] = r["value"] / r["fp8_gemm_reference_tflops"]
+                    r["peak"] = "cuBLASLt e4m3 GEMM 8192^3 through torch._scaled_mm, measured in the same run"
+                else:
+                    r["frac"] = r["value"] / peaks["burst"]
+                    r["peak"] = f"dense bf16 burst, of {peaks['source']}"
+            elif r.get("unit") == "GB/s":
+                r["frac"] = r["value"] / peaks["hbm"]
+                r["peak"] = f"HBM copy bandwidth, of {peaks['source']}"
+            out[name] = r
+        except Exception as exc:  # noqa: BLE001 — a secondary run never takes the headline down
+            out[name] = {"error": f"{type(exc).__name__}: {str(exc)[:200]}"}
+        torch.cuda.empty_cache()
+    return out
+
+
+def strong_scaling(which: str, world: int, rank: int, dev, barrier, max_over_ranks, steps: int = 20) -> dict:
+    """One FIXED problem split over the ranks with no collective: every rank builds the same tensors
+    from the same seed on its own GPU and runs the kernel on its block of (batch, KV head) units.
+      c2: B=4 H=32 S=4096 D=128 causal — the 128 (batch, head) units in contiguous blocks
+          (``sharding.shard_batch_kvheads``);
+      c3: B=8 Hq=64 Hkv=8 S=8192 D=128 causal GQA — by KV head: a rank owns Hkv/N KV heads with their
+          query heads, all batches.
+    Aggregate = the whole problem's algorithmic FLOPs over the slowest rank's time."""
+    from heddle_b200 import ops, sharding
+
+    gen = torch.Generator(device=dev).manual_seed(2024)
+    if which == "c2":
+        B, Hq, Hkv, S, D = 4, 32, 32, 4096, 128
+    else:
+        B, Hq, Hkv, S, D = 8, 64, 8, 8192, 128
+    group = Hq // Hkv
+    q = torch.randn(B, Hq, S, D, generator=gen, device=dev).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, generator=gen, device=dev).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, S, D, generator=gen, device=dev).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    if which == "c2":
+        runs = sharding.shard_batch_kvheads(B, Hkv, world, rank)  # (batch, kv_head_start, kv_head_stop)
+        views = [(q[b:b + 1, h0 * group:h1 * group], k[b:b + 1, h0:h1], v[b:b + 1, h0:h1], o[b:b + 1, h0 * group:h1 * group])
+                 for (b, h0, h1) in runs]
+        units = sum(h1 - h0 for (_, h0, h1) in runs)
+        split = "contiguous blocks of the 128 (batch, head) units"
+    else:
+        h0, h1 = sharding.shard_units(Hkv, world, rank)
+        views = [(q[:, h0 * group:h1 * group], k[:, h0:h1], v[:, h0:h1], o[:, h0 * group:h1 * group])] if h1 > h0 else []
+        units = B * (h1 - h0)
+        split = "by KV head (a rank owns Hkv/N KV heads with their query heads, all batches)"
+
+    def step():
+        for (qq, kk, vv, oo) in views:
+            ops.fa_fwd(qq, kk, vv, causal=True, out=oo)
+
+    for _ in range(3):
+        step()
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a.record()
+    for _ in range(steps):
+        step()
+    b_.record()
+    barrier()
+    ms = max_over_ranks(a.elapsed_time(b_)) / steps
+    total = 2.0 * B * Hq * S * S * D
+    pairs = units * group * ((S + 255) // 256 + 1) // 2
+    res = {"value": total / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps, "scaling": "strong",
+           "problem": f"B{B}_Hq{Hq}_Hkv{Hkv}_S{S}_D{D}_causal", "split": split, "kv_units_this_rank": units,
+           "launches_per_step_this_rank": len(views), "work_items_this_rank": pairs,
+           "note": f"{pairs} equal-cost work items for 148 persistent CTAs on this rank"
+                   + (" (less than one wave: the split, not the kernel, bounds the time)" if pairs < 148 else "")}
+    del q, k, v, o
+    torch.cuda.empty_cache()
+    return res
 
 
 # ----------------------------------------------------------------------------------------
@@ -332,7 +502,9 @@ def run_ours(args):
                 "peak_kind": f"{'sustained (power-capped clocks during the timed region)' if sustained_run else 'burst'}"
                              f" dense bf16, of {peaks['source']}",
                 "frac_of_burst_peak": achieved / peaks["burst"], "frac_of_sustained_peak": achieved / peaks["sustained"],
-                "launch_ms": launch_ms, "launch_ms_events_around_each_launch": launch_stats}
+                "launch_ms": launch_ms, "launch_ms_events_around_each_launch": launch_stats,
+                # time x median SM clock sampled during the region: lets burst, sustained and profiler runs be compared
+                "cycles_per_launch": (launch_ms * 1e-3 * clk["sm_mhz"] * 1e6) if clk["sm_mhz"] else None}
 
     # ---- the same launch in a long back-to-back loop ----------------------------------------
     # A 1 kW part drops its SM clock under the power cap after a few hundred milliseconds of this
@@ -348,9 +520,11 @@ def run_ours(args):
         s1.record()
         barrier()
     ms_long = max_over_ranks(s0.elapsed_time(s1)) / n_long
+    clk_long = clocks_long.summary()
     sustained = {"value": flops_rank * world / (ms_long * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": n_long,
-                 "ms_per_step": ms_long, "clocks": clocks_long.summary(),
-                 "frac_of_sustained_peak": flops_rank / (ms_long * 1e-3) / 1e12 / peaks["sustained"]}
+                 "ms_per_step": ms_long, "clocks": clk_long,
+                 "frac_of_sustained_peak": flops_rank / (ms_long * 1e-3) / 1e12 / peaks["sustained"],
+                 "cycles_per_launch": (ms_long * 1e-3 * clk_long["sm_mhz"] * 1e6) if clk_long["sm_mhz"] else None}
 
     # ---- end to end through the public op with host buffers --------------------------------
     # Every step moves that step's q, k, v from pinned host memory to the device and its O and
@@ -454,17 +628,26 @@ def run_ours(args):
         except Exception as exc:  # informative only
             backward = {"error": str(exc)[:120]}
 
+    # ---- strong scaling: the FIXED problems of configurations 2 and 3 split over the ranks ---------
+    strong = None
+    if distributed and not args.kernel_only:
+        strong = {"c2": strong_scaling("c2", world, rank, dev, barrier, max_over_ranks),
+                  "c3": strong_scaling("c3", world, rank, dev, barrier, max_over_ranks)}
+
+    # ---- the other configurations, short runs (N = 1) ---------------------------------------------
+    secondary = None
+    if rank == 0 and world == 1 and not args.kernel_only and not args.no_secondary:
+        secondary = run_secondary(peaks)
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "bf16_causal_mha_B4_H32_S4096_D128", "global_batch": B * world, "seq_len": S,
-                       "heads": H, "head_dim": D, "causal": True, "parallelism": f"dp{world}_batch_x_head_no_collective",
-                       "l2": "inputs+outputs (268 MB per step) exceed the 126 MB L2; no explicit flush"},
+            "config": config_dict(world),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * world,
             "clocks": clocks.summary(), "sustained": sustained, "device_status_word": status, "reference_gpu_kernel": ref_gpu,
-            "backward": backward,
+            "backward": backward, "secondary": secondary, "strong": strong,
             "pct_of_nominal_dense_bf16_peak_2250": 100.0 * value / world / 2250.0,
         }
         print(json.dumps(line), flush=True)
@@ -480,6 +663,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-reference-gpu", action="store_true",
                     help="skip timing the reference's own generated kernel (needs baseline/_ref and TileLang)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the short runs of the secondary configurations")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for profiler runs)")
     args = ap.parse_args()

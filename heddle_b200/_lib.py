@@ -138,7 +138,7 @@ class RowwiseArgs(C.Structure):
 EXPORTS = (
     "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_status_word_noalloc", "hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_rowwise_program", "hb_status_word",
     "hb_version",
-    "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma", "hb_debug_wait_timeout",
+    "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma", "hb_debug_wait_timeout", "hb_debug_fa_fwd_stages",
 )
 
 _lib = None
@@ -190,6 +190,8 @@ def load() -> C.CDLL:
     lib.hb_shutdown.restype = C.c_int
     lib.hb_debug_umma.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     lib.hb_debug_umma.restype = C.c_int
+    lib.hb_debug_fa_fwd_stages.argtypes = [C.POINTER(FaArgs), C.c_int32]
+    lib.hb_debug_fa_fwd_stages.restype = C.c_int
     lib.hb_debug_wait_timeout.argtypes = [C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]
     lib.hb_debug_wait_timeout.restype = C.c_int
     _lib = lib

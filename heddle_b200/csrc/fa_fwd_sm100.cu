@@ -43,6 +43,18 @@ static int launch_fa(const FaParams& p, int grid, int smem_optin, cudaStream_t s
   return HB_OK;
 }
 
+template <typename T, int D, int NS>
+static int launch_fa_stages(const FaParams& p, int grid, int smem_optin, cudaStream_t stream) {
+  using Smem = FaSmem<T, D, NS>;
+  if ((int)sizeof(Smem) > smem_optin) return set_error(HB_ERR_UNSUPPORTED, "hb_debug_fa_fwd_stages: not enough shared memory");
+  auto kernel = fa_fwd_kernel<T, D, NS>;
+  // set on every call: this is a diagnostic path, not worth a per-device table
+  HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+  kernel<<<grid, kFaThreads, sizeof(Smem), stream>>>(p);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB_OK;
+}
+
 static int dispatch_fa(const hb_fa_args* a, const FaParams& p, int grid, int smem_optin) {
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   if (a->dtype == HB_FP8_E4M3) return launch_fa<__nv_fp8_e4m3, 128>(p, grid, smem_optin, stream);
@@ -182,6 +194,35 @@ static int fa_fwd_impl(const hb_fa_args* a) {
   if (const char* e = getenv("HB_GRID")) grid = std::max(1, std::min(grid, atoi(e)));
 #endif
   return dispatch_fa(a, p, grid, st->smem_optin);
+}
+
+// The same kernel built with a different depth of the K/V ring (bf16, head_dim 128 only).  The
+// pipeline depth changes when tiles are loaded, never what is computed, so the results must be
+// bit-identical to hb_fa_fwd's: the test-suite uses this as its race check for the mbarrier protocol.
+static int fa_fwd_stages_impl(const hb_fa_args* a, int stages) {
+  bool empty = false;
+  int rc = fa_validate(a, "hb_debug_fa_fwd_stages", /*allow_fp8=*/false, &empty);
+  if (rc != HB_OK || empty) return rc;
+  if (a->dtype != HB_BF16 || a->D != 128)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_debug_fa_fwd_stages: bf16 with head_dim 128 only");
+  DeviceState* st = nullptr;
+  rc = get_device_state(&st);
+  if (rc != HB_OK) return rc;
+  FaParams p;
+  rc = fa_fill_params(a, "hb_debug_fa_fwd_stages", st->status_word, &p);
+  if (rc != HB_OK) return rc;
+  const int grid = std::min(p.total_pairs, st->sm_count);
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  switch (stages) {
+    case 2:
+      return launch_fa_stages<__nv_bfloat16, 128, 2>(p, grid, st->smem_optin, stream);
+    case 3:
+      return launch_fa_stages<__nv_bfloat16, 128, 3>(p, grid, st->smem_optin, stream);
+    case 5:
+      return launch_fa_stages<__nv_bfloat16, 128, 5>(p, grid, st->smem_optin, stream);
+    default:
+      return set_error(HB_ERR_UNSUPPORTED, "hb_debug_fa_fwd_stages: stages must be 2, 3 or 5 (got %d)", stages);
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -431,6 +472,11 @@ int hb_debug_set_trace(void* ptr) {
 int hb_fa_fwd_noalloc(const hb_fa_args* args) {
   hb::clear_error();
   return hb::fa_fwd_noalloc_impl(args);
+}
+
+int hb_debug_fa_fwd_stages(const hb_fa_args* args, int32_t stages) {
+  hb::clear_error();
+  return hb::fa_fwd_stages_impl(args, stages);
 }
 
 int hb_status_word_noalloc(uint32_t* out, void* stream) {

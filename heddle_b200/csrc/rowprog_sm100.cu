@@ -9,8 +9,8 @@
 // precompiled kernel interprets: nothing is compiled at run time.
 //
 // Machine, per group of 8 consecutive columns of a row (16 bytes of a 16-bit tensor):
-//   acc[8]           the running value (fp32)
-//   tmp[4][8]        saved values (HB_EW_STORE_TMP)
+//   acc[8]           the running value (fp32), in registers
+//   tmp[4][8]        saved values (HB_EW_STORE_TMP), in shared memory
 //   red[4]           row reductions computed by earlier passes (one scalar per row)
 // An instruction is `acc = op(acc, operand)`; the operand is a full input tensor (16-byte load), a
 // [cols] vector broadcast over rows, a [rows] fp32 vector broadcast over columns, an immediate, a
@@ -79,194 +79,176 @@ __device__ __forceinline__ uint4 rp_pack8(const float (&f)[8]) {
   return w;
 }
 
-// Register state of the machine for one group of 8 columns.
-struct RowProgState {
-  float acc[8];
-  float t0[8], t1[8], t2[8], t3[8];
-};
+// exp, reciprocal and friends through the MUFU: the results are rounded to 16 bits, for which the
+// approximate units (2 ulp of fp32) are exact enough, and an interpreter that has to stay under the
+// HBM roofline cannot afford the multi-instruction accurate versions.
+__device__ __forceinline__ float rp_exp(float x) { return __expf(x); }
+__device__ __forceinline__ float rp_rcp(float x) { return __fdividef(1.0f, x); }
+__device__ __forceinline__ float rp_sigmoid(float x) { return rp_rcp(1.0f + __expf(-x)); }
+__device__ __forceinline__ float rp_tanh(float x) {
+  // 1 - 2 / (1 + exp(2x)); saturates correctly for large |x| (exp -> inf gives 1, exp -> 0 gives -1)
+  return 1.0f - 2.0f * rp_rcp(1.0f + __expf(2.0f * x));
+}
 
-// Executes instructions [0, end) for the 8 columns starting at `col` of `row`.  `red` holds the
+// Register state of the machine: kG groups of 8 columns are interpreted together, so that one
+// decode serves 16 elements and a thread keeps several 16-byte loads in flight.
+constexpr int kG = 2;
+constexpr int kE = 8 * kG;
+constexpr int kRpThreads = 128;
+// The accumulator lives in registers; the temporaries, which are touched far less often and are
+// selected by a run-time index, live in shared memory ([slot][element][thread]: conflict-free).
+struct RowProgState {
+  float acc[kE];
+  float* tmp;  // this thread's column of the shared temporaries
+};
+__device__ __forceinline__ float& rp_tmp(const RowProgState& s, int slot, int e) { return s.tmp[(slot * kE + e) * kRpThreads]; }
+
+// Executes instructions [0, end) for kG groups of 8 columns: group g covers columns col[g].. of
+// row[g] (`ok[g]` false = past the end: nothing is loaded or stored for it).  `red` holds the
 // reductions of earlier passes; `store` is true in the last pass only.
 template <typename T>
-__device__ __forceinline__ void rowprog_run(const RowProgParams& p, int end, long long row, int col, const float (&red)[4],
-                                            bool store, RowProgState& s) {
+__device__ __forceinline__ void rowprog_run(const RowProgParams& p, int end, const long long (&row)[kG], const int (&col)[kG],
+                                            const bool (&ok)[kG], const float (&red)[4], bool store, RowProgState& s) {
 #pragma unroll 1
   for (int pc = 0; pc < end; ++pc) {
     const hb_ew_inst inst = p.prog[pc];
-    float v[8];
+    float v[kE];
     // ---- operand
     switch (inst.src) {
-      case HB_SRC_INPUT:
-        rp_unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.in[inst.index]) + row * p.ld_in[inst.index] + col), v);
-        break;
-      case HB_SRC_ROWVEC:
-        rp_unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.rowvec[inst.index]) + col), v);
-        break;
-      case HB_SRC_ROWSCALAR: {
-        const float x = p.rowscalar[inst.index][row];
+      case HB_SRC_INPUT: {
+        const T* base = static_cast<const T*>(p.in[inst.index]);
+        const long long ld = p.ld_in[inst.index];
+        uint4 w[kG];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = x;
+        for (int g = 0; g < kG; ++g) w[g] = ok[g] ? *reinterpret_cast<const uint4*>(base + row[g] * ld + col[g]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int g = 0; g < kG; ++g) rp_unpack8<T>(w[g], *reinterpret_cast<float(*)[8]>(&v[8 * g]));
+        break;
+      }
+      case HB_SRC_ROWVEC: {
+        const T* base = static_cast<const T*>(p.rowvec[inst.index]);
+#pragma unroll
+        for (int g = 0; g < kG; ++g) {
+          const uint4 w = ok[g] ? *reinterpret_cast<const uint4*>(base + col[g]) : make_uint4(0, 0, 0, 0);
+          rp_unpack8<T>(w, *reinterpret_cast<float(*)[8]>(&v[8 * g]));
+        }
+        break;
+      }
+      case HB_SRC_ROWSCALAR: {
+#pragma unroll
+        for (int g = 0; g < kG; ++g) {
+          const float x = ok[g] ? p.rowscalar[inst.index][row[g]] : 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[8 * g + e] = x;
+        }
         break;
       }
       case HB_SRC_TMP:
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          v[e] = inst.index == 0 ? s.t0[e] : inst.index == 1 ? s.t1[e] : inst.index == 2 ? s.t2[e] : s.t3[e];
+        for (int e = 0; e < kE; ++e) v[e] = rp_tmp(s, inst.index, e);
         break;
       case HB_SRC_REDUCED: {
         const float x = inst.index == 0 ? red[0] : inst.index == 1 ? red[1] : inst.index == 2 ? red[2] : red[3];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = x;
+        for (int e = 0; e < kE; ++e) v[e] = x;
         break;
       }
       default:  // HB_SRC_IMM, HB_SRC_NONE
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = inst.imm;
+        for (int e = 0; e < kE; ++e) v[e] = inst.imm;
         break;
     }
     // ---- operation (formulas: Heddle/heddle/frontend/codegen.py:1577-1609)
-    float (&a)[8] = s.acc;
+    float (&a)[kE] = s.acc;
+#define HB_RP_EACH(expr)              \
+  _Pragma("unroll") for (int e = 0; e < kE; ++e) { a[e] = (expr); } \
+  break
     switch (inst.op) {
-      case HB_EW_LOAD:
+      case HB_EW_LOAD: HB_RP_EACH(v[e]);
+      case HB_EW_ADD: HB_RP_EACH(a[e] + v[e]);
+      case HB_EW_SUB: HB_RP_EACH(a[e] - v[e]);
+      case HB_EW_RSUB: HB_RP_EACH(v[e] - a[e]);
+      case HB_EW_MUL: HB_RP_EACH(a[e] * v[e]);
+      case HB_EW_DIV: HB_RP_EACH(__fdividef(a[e], v[e]));
+      case HB_EW_RDIV: HB_RP_EACH(__fdividef(v[e], a[e]));
+      case HB_EW_MAX: HB_RP_EACH(fmaxf(a[e], v[e]));
+      case HB_EW_MIN: HB_RP_EACH(fminf(a[e], v[e]));
+      case HB_EW_POW: HB_RP_EACH(powf(a[e], v[e]));
+      case HB_EW_NEG: HB_RP_EACH(-a[e]);
+      case HB_EW_ABS: HB_RP_EACH(fabsf(a[e]));
+      case HB_EW_EXP: HB_RP_EACH(rp_exp(a[e]));
+      case HB_EW_LOG: HB_RP_EACH(__logf(a[e]));
+      case HB_EW_LOG2: HB_RP_EACH(__log2f(a[e]));
+      case HB_EW_SQRT: HB_RP_EACH(sqrtf(a[e]));
+      case HB_EW_RSQRT: HB_RP_EACH(rsqrtf(a[e]));
+      case HB_EW_RECIP: HB_RP_EACH(rp_rcp(a[e]));
+      case HB_EW_SIGMOID: HB_RP_EACH(rp_sigmoid(a[e]));
+      case HB_EW_SILU: HB_RP_EACH(a[e] * rp_sigmoid(a[e]));
+      case HB_EW_RELU: HB_RP_EACH(fmaxf(a[e], 0.0f));
+      case HB_EW_GELU_TANH: HB_RP_EACH(a[e] * 0.5f * (1.0f + rp_tanh(0.7978845608f * (a[e] + 0.044715f * a[e] * a[e] * a[e]))));
+      case HB_EW_GELU_ERF: HB_RP_EACH(a[e] * 0.5f * (1.0f + erff(a[e] * 0.7071067811865476f)));
+      case HB_EW_TANH: HB_RP_EACH(rp_tanh(a[e]));
+      case HB_EW_ROUND:
 #pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = v[e];
-        break;
-      case HB_EW_ADD:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = a[e] + v[e];
-        break;
-      case HB_EW_SUB:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = a[e] - v[e];
-        break;
-      case HB_EW_RSUB:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = v[e] - a[e];
-        break;
-      case HB_EW_MUL:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = a[e] * v[e];
-        break;
-      case HB_EW_DIV:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = a[e] / v[e];
-        break;
-      case HB_EW_RDIV:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = v[e] / a[e];
-        break;
-      case HB_EW_MAX:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = fmaxf(a[e], v[e]);
-        break;
-      case HB_EW_MIN:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = fminf(a[e], v[e]);
-        break;
-      case HB_EW_POW:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = powf(a[e], v[e]);
-        break;
-      case HB_EW_NEG:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = -a[e];
-        break;
-      case HB_EW_ABS:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = fabsf(a[e]);
-        break;
-      case HB_EW_EXP:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = expf(a[e]);
-        break;
-      case HB_EW_LOG:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = logf(a[e]);
-        break;
-      case HB_EW_LOG2:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = log2f(a[e]);
-        break;
-      case HB_EW_SQRT:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = sqrtf(a[e]);
-        break;
-      case HB_EW_RSQRT:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = 1.0f / sqrtf(a[e]);
-        break;
-      case HB_EW_RECIP:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = 1.0f / a[e];
-        break;
-      case HB_EW_SIGMOID:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = 1.0f / (1.0f + expf(-a[e]));
-        break;
-      case HB_EW_SILU:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = a[e] * (1.0f / (1.0f + expf(-a[e])));
-        break;
-      case HB_EW_RELU:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = fmaxf(a[e], 0.0f);
-        break;
-      case HB_EW_GELU_TANH:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = a[e] * 0.5f * (1.0f + tanhf(0.7978845608f * (a[e] + 0.044715f * a[e] * a[e] * a[e])));
-        break;
-      case HB_EW_GELU_ERF:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = a[e] * 0.5f * (1.0f + erff(a[e] * 0.7071067811865476f));
-        break;
-      case HB_EW_TANH:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] = tanhf(a[e]);
-        break;
-      case HB_EW_ROUND: {
-        const uint4 w = rp_pack8<T>(a);
-        rp_unpack8<T>(w, a);
-        break;
-      }
-      case HB_EW_STORE_TMP:
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          if (inst.index == 0) s.t0[e] = a[e];
-          else if (inst.index == 1) s.t1[e] = a[e];
-          else if (inst.index == 2) s.t2[e] = a[e];
-          else s.t3[e] = a[e];
+        for (int g = 0; g < kG; ++g) {
+          float (&ag)[8] = *reinterpret_cast<float(*)[8]>(&a[8 * g]);
+          const uint4 w = rp_pack8<T>(ag);
+          rp_unpack8<T>(w, ag);
         }
         break;
+      case HB_EW_STORE_TMP:
+#pragma unroll
+        for (int e = 0; e < kE; ++e) rp_tmp(s, inst.index, e) = a[e];
+        break;
       case HB_EW_STORE_OUT:
-        if (store)
-          *reinterpret_cast<uint4*>(static_cast<T*>(p.out[inst.index]) + row * p.ld_out[inst.index] + col) = rp_pack8<T>(a);
+        if (store) {
+          T* base = static_cast<T*>(p.out[inst.index]);
+          const long long ld = p.ld_out[inst.index];
+#pragma unroll
+          for (int g = 0; g < kG; ++g) {
+            if (ok[g]) *reinterpret_cast<uint4*>(base + row[g] * ld + col[g]) = rp_pack8<T>(*reinterpret_cast<float(*)[8]>(&a[8 * g]));
+          }
+        }
         break;
       default:  // HB_EW_REDUCE_*: a no-op inside a pass (the pass that ends here reduces acc afterwards)
         break;
     }
+#undef HB_RP_EACH
   }
 }
 
 // No reductions: a flat stream over the 16-byte groups of the matrix.
 template <typename T>
-__global__ void __launch_bounds__(256) rowprog_stream_kernel(const __grid_constant__ RowProgParams p) {
+__global__ void __launch_bounds__(kRpThreads) rowprog_stream_kernel(const __grid_constant__ RowProgParams p) {
+  __shared__ float tmp_s[HB_EW_MAX_TMP * kE * kRpThreads];
   const int groups = p.cols >> 3;
   const long long total = p.rows * groups;
   const float red[4] = {0.f, 0.f, 0.f, 0.f};
-  for (long long g = blockIdx.x * 256ll + threadIdx.x; g < total; g += 256ll * gridDim.x) {
-    const long long row = g / groups;
-    const int col = static_cast<int>(g - row * groups) << 3;
+  // a thread takes kG groups that are one block width apart, so that a warp's loads stay contiguous
+  for (long long g0 = blockIdx.x * (1ll * kRpThreads * kG) + threadIdx.x; g0 < total; g0 += 1ll * kRpThreads * kG * gridDim.x) {
+    long long row[kG];
+    int col[kG];
+    bool ok[kG];
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      const long long idx = g0 + 1ll * kRpThreads * g;
+      ok[g] = idx < total;
+      row[g] = ok[g] ? idx / groups : 0;
+      col[g] = ok[g] ? static_cast<int>(idx - row[g] * groups) << 3 : 0;
+    }
     RowProgState s;
-    rowprog_run<T>(p, p.n_inst, row, col, red, true, s);
+    s.tmp = tmp_s + threadIdx.x;
+    rowprog_run<T>(p, p.n_inst, row, col, ok, red, true, s);
   }
 }
 
 // With reductions: kWarpsPerRow warps (1 or 4) own a row; 128-thread CTAs.
 template <typename T, int kWarpsPerRow>
-__global__ void __launch_bounds__(128) rowprog_reduce_kernel(const __grid_constant__ RowProgParams p) {
+__global__ void __launch_bounds__(kRpThreads) rowprog_reduce_kernel(const __grid_constant__ RowProgParams p) {
   constexpr int kThreadsPerRow = 32 * kWarpsPerRow;
   constexpr int kRowsPerCta = 4 / kWarpsPerRow;
   __shared__ float part[4];
+  __shared__ float tmp_s[HB_EW_MAX_TMP * kE * kRpThreads];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long row = kWarpsPerRow == 1 ? (blockIdx.x * static_cast<long long>(kRowsPerCta) + warp) : static_cast<long long>(blockIdx.x);
   const int t = kWarpsPerRow == 1 ? lane : static_cast<int>(threadIdx.x);
@@ -280,12 +262,28 @@ __global__ void __launch_bounds__(128) rowprog_reduce_kernel(const __grid_consta
     const int kind = last ? 0 : p.prog[end].op;
     float partial = (kind == HB_EW_REDUCE_MAX) ? -INFINITY : 0.f;
     if (row_ok) {
-      for (int g = t; g < groups; g += kThreadsPerRow) {
+      for (int g0 = t; g0 < groups; g0 += kThreadsPerRow * kG) {
+        long long rows_[kG];
+        int col[kG];
+        bool ok[kG];
+#pragma unroll
+        for (int g = 0; g < kG; ++g) {
+          const int gi = g0 + kThreadsPerRow * g;
+          ok[g] = gi < groups;
+          rows_[g] = row;
+          col[g] = ok[g] ? gi << 3 : 0;
+        }
         RowProgState s;
-        rowprog_run<T>(p, end, row, g << 3, red, last, s);
+        s.tmp = tmp_s + threadIdx.x;
+        rowprog_run<T>(p, end, rows_, col, ok, red, last, s);
         if (!last) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) partial = (kind == HB_EW_REDUCE_MAX) ? fmaxf(partial, s.acc[e]) : partial + s.acc[e];
+          for (int g = 0; g < kG; ++g) {
+            if (!ok[g]) continue;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              partial = (kind == HB_EW_REDUCE_MAX) ? fmaxf(partial, s.acc[8 * g + e]) : partial + s.acc[8 * g + e];
+          }
         }
       }
     }
@@ -411,9 +409,10 @@ static int rowprog_impl(const hb_rowwise_args* a) {
   const bool bf16 = a->dtype == HB_BF16;
   if (p.n_red == 0) {
     const long long groups = a->rows * (a->cols / 8);
-    const unsigned grid = static_cast<unsigned>(std::min<long long>((groups + 255) / 256, 32ll * st->sm_count));
-    if (bf16) rowprog_stream_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
-    else rowprog_stream_kernel<__half><<<grid, 256, 0, stream>>>(p);
+    const long long per_block = 1ll * kRpThreads * kG;
+    const unsigned grid = static_cast<unsigned>(std::min<long long>((groups + per_block - 1) / per_block, 48ll * st->sm_count));
+    if (bf16) rowprog_stream_kernel<__nv_bfloat16><<<grid, kRpThreads, 0, stream>>>(p);
+    else rowprog_stream_kernel<__half><<<grid, kRpThreads, 0, stream>>>(p);
   } else if (a->cols <= 1024) {
     const unsigned grid = static_cast<unsigned>((a->rows + 3) / 4);
     if (bf16) rowprog_reduce_kernel<__nv_bfloat16, 1><<<grid, 128, 0, stream>>>(p);

@@ -38,6 +38,7 @@ def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = 
            softmax_scale: Optional[float] = None, layout: str = "bhsd", return_lse: bool = False,
            out: Optional[torch.Tensor] = None,
            scales: Optional[Tuple[float, float, float]] = None,
+           debug_stages: Optional[int] = None,
            ) -> "torch.Tensor | Tuple[torch.Tensor, torch.Tensor]":
     """FlashAttention forward through ``hb_fa_fwd``.
 
@@ -46,6 +47,8 @@ def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = 
     have fewer heads than Q (grouped-query attention).  Returns O in the layout and
     dtype of q (bf16 for FP8 inputs) and, if requested, the natural-log LSE
     [B, Hq, Sq] in fp32.  ``scales`` = (q, k, v) per-tensor dequantisation scales for FP8.
+    ``debug_stages`` (2, 3 or 5; bf16, head_dim 128) runs the kernel built with that depth of the K/V
+    ring (``hb_debug_fa_fwd_stages``): results must not depend on it.
     """
     _require_cuda(q, k, v)
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
@@ -87,7 +90,10 @@ def fa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = 
         a.q_scale, a.k_scale, a.v_scale = (float(x) for x in scales)
     a.stream = _stream_ptr(q.device)
     with torch.cuda.device(q.device):
-        _lib.check(_lib.load().hb_fa_fwd(C.byref(a)))
+        if debug_stages is None:
+            _lib.check(_lib.load().hb_fa_fwd(C.byref(a)))
+        else:
+            _lib.check(_lib.load().hb_debug_fa_fwd_stages(C.byref(a), int(debug_stages)))
     return (out, lse) if return_lse else out
 
 

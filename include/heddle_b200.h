@@ -425,6 +425,15 @@ int hb_debug_umma(int mode, const void* a, const void* b, float* out, int32_t kn
                   void* stream);
 
 /*
+ * hb_fa_fwd with the K/V ring of the kernel built `stages` deep (2, 3 or 5; bf16, head_dim 128).
+ * The depth only changes when tiles are loaded, so O and LSE must be bit-identical to hb_fa_fwd's
+ * (which uses 5): a mismatch means a race in the barrier protocol.  The reference plans the same
+ * stand-in for a race detector ("bitwise comparison between a 1-stage and an N-stage pipeline
+ * build"); it has no counterpart there.
+ */
+int hb_debug_fa_fwd_stages(const hb_fa_args* args, int32_t stages);
+
+/*
  * Failure-detection probe: one small CTA waits on a barrier that is never signalled, with a
  * limit of limit_us microseconds (1..100000).  The wait gives up, raises the CTA's abort flag and
  * records kStatusWaitTimeout | role (0x170) in a scratch status word, a second warp leaves its own
