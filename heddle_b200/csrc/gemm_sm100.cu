@@ -115,6 +115,14 @@ static int gemm_impl(const hb_gemm_args* a) {
     rc = encode_tensor_map(&p.tm_w, dt, 3, a->w, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HB_OK) return rc;
   }
+  if (epi_class == kEpiPlain) {
+    const uint32_t box[3] = {64, (uint32_t)kGemmBM, 1};
+    const uint64_t dims[3] = {(uint64_t)n_out, (uint64_t)a->M, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)a->ldo * 2, (uint64_t)o_bs * 2};
+    rc = encode_tensor_map(&p.tm_out, dt, 3, a->out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB_OK) return rc;
+    p.tma_store = 1;
+  }
   p.out = a->out;
   p.row_scale = a->row_scale;
   p.residual = a->residual;

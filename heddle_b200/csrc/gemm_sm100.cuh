@@ -47,6 +47,7 @@ enum GemmRole : uint32_t { kGemmRoleTma = 0x21, kGemmRoleMma = 0x22, kGemmRoleEp
 struct alignas(64) GemmParams {
   CUtensorMap tm_a;
   CUtensorMap tm_w;
+  CUtensorMap tm_out;  // PLAIN epilogue: [N_out, M, batch] tiles of 64 columns x 128 rows, stored by TMA
   void* out;
   const float* row_scale;
   const void* residual;
@@ -65,11 +66,14 @@ struct alignas(64) GemmParams {
   int tiles_per_batch;
   int w_kn;           // 1: the second operand is [K, N] row-major
   long long o_batch_stride, r_batch_stride;  // elements between consecutive batches of out / residual
+  int tma_store;      // PLAIN epilogue: results leave through shared memory and a TMA store
 };
 
 struct GemmSmem {
   alignas(1024) uint8_t a[kGemmStages][kGemmBM * kGemmBK * 2];
   alignas(1024) uint8_t b[kGemmStages][kGemmBN * kGemmBK * 2];
+  // one 128-row x 64-column (128-byte rows, 128B-swizzled) output slab per epilogue warpgroup
+  alignas(1024) uint8_t stage_out[2][kGemmBM * 128];
   uint64_t full[kGemmStages], empty[kGemmStages];
   uint64_t acc_full[2], acc_empty[2];
   uint64_t drain;
@@ -153,6 +157,19 @@ __device__ __forceinline__ void store8(const GemmParams& p, int b, int row, int 
   *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + b * p.o_batch_stride + (long long)row * p.ldo + col) = pack8<T>(v);
 }
 
+// Adds the residual (if any) to 8 consecutive values of one row.
+template <typename T>
+__device__ __forceinline__ void add_residual8(const GemmParams& p, int b, int row, int col, float (&v)[8]) {
+  if (p.residual != nullptr) {
+    float r[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + b * p.r_batch_stride +
+                                               (long long)row * p.ldr + col),
+               r);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] += r[i];
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ void load_bias8(const GemmParams& p, int col, float (&b)[8]) {
   unpack8<T>(*reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + col), b);
@@ -163,46 +180,80 @@ __device__ __forceinline__ void load_bias8(const GemmParams& p, int col, float (
 // tile: `part` (0 or 1) selects this thread's half of the output columns.
 template <typename T, int EPI>
 __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t tacc, int b, int m0, int n0,
-                                                  int row_in_tile, int part) {
+                                                  int row_in_tile, int part, uint8_t* stage_base, uint64_t* release) {
   const int row = m0 + row_in_tile;
   const bool row_ok = row < p.M;
   const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[(long long)b * p.M + row] : 1.0f;
 
   if constexpr (EPI == kEpiPlain) {
-#pragma unroll 1
-    for (int c = part * (kGemmBN / 64); c < (part + 1) * (kGemmBN / 64); ++c) {
-      uint32_t r[32];
-      __syncwarp();  // reconverge after the predicated stores of the previous chunk
-      tmem_ld32(tacc + c * 32, r);
-      tmem_wait_ld();
-      const int col = n0 + c * 32;
-      if (!row_ok || col >= p.N_out) continue;
+    // The thread's half row of the accumulator (128 columns) is read with ONE wait: a TMEM load issued
+    // while the tensor pipe is busy queues behind the MMAs in flight (its latency is then well over a
+    // thousand cycles), so the loads are issued together and the accumulator buffer is handed back to
+    // the MMA warp as soon as they have landed, before any arithmetic or store.
+    uint32_t r[4][32];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        if (col + g * 8 >= p.N_out) break;
-        float v[8];
+    for (int h = 0; h < 4; ++h) tmem_ld32(tacc + part * (kGemmBN / 2) + h * 32, r[h]);
+    tmem_wait_ld();
+    tc_fence_before();
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(release);
+    // Coalesced stores: the warpgroup's 128 rows x 64 columns go to shared memory in the 128-byte
+    // swizzled layout (a thread writes its own row: conflict-free), one thread hands the slab to the
+    // TMA, which clips rows past M and columns past N_out.  Two slabs per tile and warpgroup.
+    uint8_t* stage = stage_base;
+    const bool issuer = row_in_tile == 0;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g * 8 + e]) * rs;
-        if (p.bias != nullptr) {
-          float b[8];
-          load_bias8<T>(p, col + g * 8, b);
+    for (int cc = 0; cc < 2; ++cc) {
+      const int col0 = n0 + part * (kGemmBN / 2) + cc * 64;
+      if (issuer) tma_store_wait_read<0>();  // the previous slab has left shared memory
+      named_bar_sync(1 + part, 128);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] += b[e];
+      for (int h = 0; h < 2; ++h) {
+        const int col = col0 + h * 32;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[cc * 2 + h][g * 8 + e]) * rs;
+          const bool live = row_ok && col + g * 8 < p.N_out;
+          if (p.bias != nullptr && col + g * 8 < p.N_out) {
+            float bb[8];
+            load_bias8<T>(p, col + g * 8, bb);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += bb[e];
+          }
+          if (p.act != kActNone) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = apply_act(v[e], p.act);
+          }
+          if (live) add_residual8<T>(p, b, row, col + g * 8, v);
+          const int chunk = (h * 4 + g) ^ (row_in_tile & 7);
+          *reinterpret_cast<uint4*>(stage + row_in_tile * 128 + chunk * 16) = pack8<T>(v);
         }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = apply_act(v[e], p.act);
-        store8<T>(p, b, row, col + g * 8, v);
+      }
+      fence_proxy_async();
+      named_bar_sync(1 + part, 128);
+      if (issuer && col0 < p.N_out) {
+        tma_store_3d(&p.tm_out, stage, col0, m0, b);
+        tma_store_commit();
       }
     }
   } else if constexpr (EPI == kEpiSwiglu) {
-#pragma unroll 1
-    for (int c = part * 2; c < part * 2 + 2; ++c) {
-      uint32_t rg[32], ru[32];
-      __syncwarp();
-      tmem_ld32(tacc + c * 32, rg);
-      tmem_ld32(tacc + 128 + c * 32, ru);
-      tmem_wait_ld();
-      const int col = n0 + c * 32;
+    // gate and up columns of this thread's half row, read with one wait (see the plain epilogue) and the
+    // accumulator released before the arithmetic
+    uint32_t rg[2][32], ru[2][32];
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      tmem_ld32(tacc + (part * 2 + cc) * 32, rg[cc]);
+      tmem_ld32(tacc + 128 + (part * 2 + cc) * 32, ru[cc]);
+    }
+    tmem_wait_ld();
+    tc_fence_before();
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(release);
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const int col = n0 + (part * 2 + cc) * 32;
       if (!row_ok || col >= p.N_out) continue;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
@@ -210,8 +261,8 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
         float v[8], u[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          v[e] = __uint_as_float(rg[g * 8 + e]) * rs;
-          u[e] = __uint_as_float(ru[g * 8 + e]) * rs;
+          v[e] = __uint_as_float(rg[cc][g * 8 + e]) * rs;
+          u[e] = __uint_as_float(ru[cc][g * 8 + e]) * rs;
         }
         if (p.bias != nullptr) {
           float bg[8], bu[8];
@@ -238,54 +289,81 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
     const bool split_heads = hd <= kGemmBN / 2;
     const int h_begin = split_heads ? part * (kGemmBN / 2) : 0, h_end = split_heads ? h_begin + kGemmBN / 2 : kGemmBN;
     const int c_begin = split_heads ? 0 : part * (half / 2), c_end = split_heads ? half : c_begin + half / 2;
-#pragma unroll 1
-    for (int h0 = h_begin; h0 < h_end; h0 += hd) {
-#pragma unroll 1
-      for (int c = c_begin; c < c_end; c += 32) {
-        uint32_t r1[32], r2[32];
-        __syncwarp();
-        tmem_ld32(tacc + h0 + c, r1);
-        tmem_ld32(tacc + h0 + half + c, r2);
-        tmem_wait_ld();
-        const int col = n0 + h0 + c;
-        if (!row_ok || col >= p.N_out) continue;
-        const bool rotate = col < p.rope_cols;
+    // rotation of 32 column pairs (x1 = columns h0 + c .., x2 = the same columns half a head further)
+    auto rotate_store = [&](const uint32_t (&r1)[32], const uint32_t (&r2)[32], int h0, int c) {
+      const int col = n0 + h0 + c;
+      if (!row_ok || col >= p.N_out) return;
+      const bool rotate = col < p.rope_cols;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float x1[8], x2[8];
+      for (int g = 0; g < 4; ++g) {
+        float x1[8], x2[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          x1[e] = __uint_as_float(r1[g * 8 + e]) * rs;
+          x2[e] = __uint_as_float(r2[g * 8 + e]) * rs;
+        }
+        if (p.bias != nullptr) {
+          float b1[8], b2[8];
+          load_bias8<T>(p, col + g * 8, b1);
+          load_bias8<T>(p, col + half + g * 8, b2);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            x1[e] = __uint_as_float(r1[g * 8 + e]) * rs;
-            x2[e] = __uint_as_float(r2[g * 8 + e]) * rs;
+            x1[e] += b1[e];
+            x2[e] += b2[e];
           }
-          if (p.bias != nullptr) {
-            float b1[8], b2[8];
-            load_bias8<T>(p, col + g * 8, b1);
-            load_bias8<T>(p, col + half + g * 8, b2);
+        }
+        if (rotate) {
+          // eight consecutive angles as two 16-byte loads per table (rows are 16-byte aligned:
+          // head_dim / 2 is a multiple of 32)
+          const float4 c0 = *reinterpret_cast<const float4*>(cosr + c + g * 8), c1 = *reinterpret_cast<const float4*>(cosr + c + g * 8 + 4);
+          const float4 s0 = *reinterpret_cast<const float4*>(sinr + c + g * 8), s1 = *reinterpret_cast<const float4*>(sinr + c + g * 8 + 4);
+          const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              x1[e] += b1[e];
-              x2[e] += b2[e];
-            }
+          for (int e = 0; e < 8; ++e) {
+            const float xa = x1[e], xb = x2[e];
+            x1[e] = xa * cs[e] - xb * sn[e];
+            x2[e] = xb * cs[e] + xa * sn[e];
           }
-          if (rotate) {
-            // eight consecutive angles as two 16-byte loads per table (rows are 16-byte aligned:
-            // head_dim / 2 is a multiple of 32)
-            const float4 c0 = *reinterpret_cast<const float4*>(cosr + c + g * 8), c1 = *reinterpret_cast<const float4*>(cosr + c + g * 8 + 4);
-            const float4 s0 = *reinterpret_cast<const float4*>(sinr + c + g * 8), s1 = *reinterpret_cast<const float4*>(sinr + c + g * 8 + 4);
-            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        }
+        store8<T>(p, b, row, col + g * 8, x1);
+        store8<T>(p, b, row, col + half + g * 8, x2);
+      }
+    };
+    auto release_acc = [&]() {
+      tc_fence_before();
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(release);
+    };
+    if (split_heads) {
+      // head_dim 64 or 128: the warpgroup's 128 columns are read with one wait and the accumulator is
+      // released before the arithmetic (see the plain epilogue)
+      uint32_t r[4][32];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float a = x1[e], b = x2[e];
-              x1[e] = a * cs[e] - b * sn[e];
-              x2[e] = b * cs[e] + a * sn[e];
-            }
-          }
-          store8<T>(p, b, row, col + g * 8, x1);
-          store8<T>(p, b, row, col + half + g * 8, x2);
+      for (int h = 0; h < 4; ++h) tmem_ld32(tacc + h_begin + h * 32, r[h]);
+      tmem_wait_ld();
+      release_acc();
+      if (hd == 128) {
+        rotate_store(r[0], r[2], h_begin, 0);
+        rotate_store(r[1], r[3], h_begin, 32);
+      } else {
+        rotate_store(r[0], r[1], h_begin, 0);
+        rotate_store(r[2], r[3], h_begin + 64, 0);
+      }
+    } else {
+#pragma unroll 1
+      for (int h0 = h_begin; h0 < h_end; h0 += hd) {
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; c += 32) {
+          uint32_t r1[32], r2[32];
+          __syncwarp();
+          tmem_ld32(tacc + h0 + c, r1);
+          tmem_ld32(tacc + h0 + half + c, r2);
+          tmem_wait_ld();
+          rotate_store(r1, r2, h0, c);
         }
       }
+      release_acc();
     }
   }
 }
@@ -312,6 +390,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     if ((smem_u32(smem_raw) & 1023u) != 0u) raise_abort(ctx, kStatusSmemMisaligned);
     prefetch_tensormap(&p.tm_a);
     prefetch_tensormap(&p.tm_w);
+    if (p.tma_store) prefetch_tensormap(&p.tm_out);
   }
   if (warp == 1) {
     tmem_alloc(&s.tmem_base, 512);
@@ -426,11 +505,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       if (!mbar_wait_warp(&s.acc_full[acc], (tile_i >> 1) & 1, ctx, kGemmRoleEpi)) break;
       tc_fence_after();
       gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, b, m_t * kGemmBM, n_t * p.tile_cols,
-                                quarter * 32 + lane, (warp - 2) >> 2);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s.acc_empty[acc]);
+                                quarter * 32 + lane, (warp - 2) >> 2, s.stage_out[(warp - 2) >> 2], &s.acc_empty[acc]);
+      // the epilogue hands the accumulator buffer back itself (acc_empty), as soon as it has read it
     }
+    // the slabs handed to the TMA must have been written out before shared memory goes away
+    if (p.tma_store && quarter == 0 && lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before();

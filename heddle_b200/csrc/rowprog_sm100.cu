@@ -221,20 +221,29 @@ __device__ __forceinline__ void rowprog_run(const RowProgParams& p, int end, con
 template <typename T>
 __global__ void __launch_bounds__(kRpThreads) rowprog_stream_kernel(const __grid_constant__ RowProgParams p) {
   __shared__ float tmp_s[HB_EW_MAX_TMP * kE * kRpThreads];
-  const int groups = p.cols >> 3;
-  const long long total = p.rows * groups;
+  const unsigned groups = static_cast<unsigned>(p.cols >> 3);
+  const unsigned total = static_cast<unsigned>(p.rows) * groups;  // the host checks that this fits 32 bits
   const float red[4] = {0.f, 0.f, 0.f, 0.f};
-  // a thread takes kG groups that are one block width apart, so that a warp's loads stay contiguous
-  for (long long g0 = blockIdx.x * (1ll * kRpThreads * kG) + threadIdx.x; g0 < total; g0 += 1ll * kRpThreads * kG * gridDim.x) {
+  // a thread takes kG groups that are one block width apart, so that a warp's loads stay contiguous;
+  // 32-bit index arithmetic (a 64-bit division per group would cost more than the program itself)
+  const unsigned stride = kRpThreads * kG * gridDim.x;
+  for (unsigned g0 = blockIdx.x * (kRpThreads * kG) + threadIdx.x; g0 < total; g0 += stride) {
     long long row[kG];
     int col[kG];
     bool ok[kG];
 #pragma unroll
     for (int g = 0; g < kG; ++g) {
-      const long long idx = g0 + 1ll * kRpThreads * g;
-      ok[g] = idx < total;
-      row[g] = ok[g] ? idx / groups : 0;
-      col[g] = ok[g] ? static_cast<int>(idx - row[g] * groups) << 3 : 0;
+      const unsigned idx = g0 + kRpThreads * g;
+      ok[g] = idx < total && idx >= g0;  // the second test guards the 32-bit wrap of the last batch
+      const unsigned r = ok[g] ? idx / groups : 0u;
+      row[g] = r;
+      col[g] = ok[g] ? static_cast<int>(idx - r * groups) << 3 : 0;
+    }
+    if (g0 + stride < g0) {  // next index would wrap: this was the last batch of this thread
+      RowProgState s;
+      s.tmp = tmp_s + threadIdx.x;
+      rowprog_run<T>(p, p.n_inst, row, col, ok, red, true, s);
+      break;
     }
     RowProgState s;
     s.tmp = tmp_s + threadIdx.x;
@@ -318,7 +327,8 @@ static int rowprog_impl(const hb_rowwise_args* a) {
   if (a->dtype != HB_BF16 && a->dtype != HB_FP16)
     return set_error(HB_ERR_UNSUPPORTED, "hb_rowwise_program: dtype %d not supported (bf16, fp16)", a->dtype);
   if (a->cols % 8 != 0) return set_error(HB_ERR_UNSUPPORTED, "hb_rowwise_program: cols must be a multiple of 8 (got %d)", a->cols);
-  if (a->rows > 0x7fffffffLL) return set_error(HB_ERR_UNSUPPORTED, "hb_rowwise_program: too many rows");
+  if (a->rows > 0x7fffffffLL || a->rows * (a->cols / 8) > 0xffffffffLL)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_rowwise_program: too many rows or elements (at most 2^31-1 rows and 2^35 elements)");
   if (a->n_inputs < 0 || a->n_inputs > HB_EW_MAX_INPUTS || a->n_rowvec < 0 || a->n_rowvec > HB_EW_MAX_ROWVEC ||
       a->n_rowscalar < 0 || a->n_rowscalar > HB_EW_MAX_ROWSCALAR || a->n_outputs < 1 || a->n_outputs > HB_EW_MAX_OUTPUTS)
     return set_error(HB_ERR_BAD_ARG, "hb_rowwise_program: operand counts out of range");
