@@ -374,8 +374,13 @@ def strong_scaling(which: str, world: int, rank: int, dev, barrier, max_over_ran
     o = torch.empty_like(q)
     if which == "c2":
         runs = sharding.shard_batch_kvheads(B, Hkv, world, rank)  # (batch, kv_head_start, kv_head_stop)
-        views = [(q[b:b + 1, h0 * group:h1 * group], k[b:b + 1, h0:h1], v[b:b + 1, h0:h1], o[b:b + 1, h0 * group:h1 * group])
-                 for (b, h0, h1) in runs]
+        if runs and all(h0 == 0 and h1 == Hkv for (_, h0, h1) in runs):
+            # whole batch elements: one launch on the [b0:b1] slice
+            b0, b1 = runs[0][0], runs[-1][0] + 1
+            views = [(q[b0:b1], k[b0:b1], v[b0:b1], o[b0:b1])]
+        else:
+            views = [(q[b:b + 1, h0 * group:h1 * group], k[b:b + 1, h0:h1], v[b:b + 1, h0:h1], o[b:b + 1, h0 * group:h1 * group])
+                     for (b, h0, h1) in runs]
         units = sum(h1 - h0 for (_, h0, h1) in runs)
         split = "contiguous blocks of the 128 (batch, head) units"
     else:
@@ -399,7 +404,7 @@ def strong_scaling(which: str, world: int, rank: int, dev, barrier, max_over_ran
     barrier()
     ms = max_over_ranks(a.elapsed_time(b_)) / steps
     total = 2.0 * B * Hq * S * S * D
-    pairs = units * group * ((S + 255) // 256 + 1) // 2
+    pairs = units * group * (((S + 255) // 256 + 1) // 2)
     res = {"value": total / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps, "scaling": "strong",
            "problem": f"B{B}_Hq{Hq}_Hkv{Hkv}_S{S}_D{D}_causal", "split": split, "kv_units_this_rank": units,
            "launches_per_step_this_rank": len(views), "work_items_this_rank": pairs,

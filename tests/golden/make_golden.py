@@ -67,6 +67,26 @@ class Attn(torch.nn.Module):
         return torch.matmul(torch.softmax(s, dim=-1), v)
 
 
+class H2O(torch.nn.Module):
+    """The H2O structure the reference fuses (Heddle/heddle/frontend/backend.py:1316-1419): causal attention whose
+    probabilities also feed a sum over the query axis.  With the fusion switched off the reference executes
+    this graph eagerly, which is the same arithmetic as the PyTorch fallback of its fused leaf (:186-201)."""
+
+    def forward(self, q, k, v):
+        Sq, Skv = q.shape[-2], k.shape[-2]
+        s = torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(q.shape[-1])
+        s = s + torch.triu(torch.full((Sq, Skv), float("-inf")), diagonal=Skv - Sq + 1)
+        p = torch.softmax(s, dim=-1)
+        return torch.matmul(p, v), p.sum(dim=-2)
+
+
+def run_reference_all(module: torch.nn.Module, *inputs: torch.Tensor):
+    torch._dynamo.reset()
+    compiled = torch.compile(module, backend=tilelang_backend)
+    with torch.no_grad():
+        return tuple(t.detach().clone() for t in compiled(*inputs))
+
+
 class LinearAct(torch.nn.Module):
     def __init__(self, w, act):
         super().__init__()
@@ -124,6 +144,12 @@ def main() -> None:
     xs = torch.randn(2, 128, 256, generator=gx).to(torch.bfloat16).float()
     out["llama_small"] = dict(seed=4, x_seed=5, checksum=float(xs.double().sum()),
                               out=run_reference(layer, xs))
+    # H2O: causal attention + column sums of the probabilities, keys longer than queries (seed 6)
+    q, k, v = O.make_qkv(1, 2, 2, 160, 288, 64, seed=6, dtype=torch.bfloat16)
+    h2o_out, h2o_score = run_reference_all(H2O(), q.float(), k.float(), v.float())
+    out["h2o"] = dict(shape=(1, 2, 2, 160, 288, 64), seed=6, causal=True, in_dtype="bfloat16",
+                      checksum=float(q.double().sum() + k.double().sum() + v.double().sum()),
+                      out=h2o_out, score=h2o_score)
     torch.save(out, HERE / "reference_outputs.pt")
     for name, case in out.items():
         o = case.get("out")

@@ -35,6 +35,17 @@ def test_h2o_score_matches_oracle(ops, B, Hq, Hkv, Sq, Skv, D, causal, dtype):
     assert (score.cpu() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
 
 
+def test_h2o_matches_reference_fixture(ops, golden):
+    """Against the outputs the reference's own backend produced for the H2O structure (fusion off)."""
+    case = golden["h2o"]
+    B, Hq, Hkv, Sq, Skv, D = case["shape"]
+    q, k, v = (t.cuda() for t in O.make_qkv(B, Hq, Hkv, Sq, Skv, D, seed=case["seed"], dtype=torch.bfloat16))
+    out, lse = ops.fa_fwd(q, k, v, causal=True, return_lse=True)
+    score = ops.h2o_score(q, k, lse, causal=True)
+    assert (out.float().cpu() - case["out"]).abs().max().item() <= 2e-2
+    assert (score.cpu() - case["score"]).abs().max().item() <= 2e-2 * max(1.0, case["score"].abs().max().item())
+
+
 def test_h2o_leaf_and_factories(ops):
     from heddle_b200.frontend.backend import _tilelang_h2o_attention
     from heddle_b200.tileop import flashattn_lse, h2o_score

@@ -73,6 +73,20 @@ def test_h2o_score_columns_sum_to_rows():
     assert (score - torch.softmax(s, -1).sum(-2)).abs().max().item() <= 1e-5
 
 
+def test_h2o_matches_reference_capture(golden):
+    """The H2O structure run eagerly by the reference's own backend (fusion off): attention output and
+    the column sums of the probabilities, keys longer than queries."""
+    case = golden["h2o"]
+    B, Hq, Hkv, Sq, Skv, D = case["shape"]
+    q, k, v = O.make_qkv(B, Hq, Hkv, Sq, Skv, D, seed=case["seed"], dtype=torch.bfloat16)
+    assert float(q.double().sum() + k.double().sum() + v.double().sum()) == pytest.approx(case["checksum"], rel=1e-12)
+    out, lse = O.attention_eager(q, k, v, causal=True)
+    assert (out - case["out"]).abs().max().item() <= 2e-6
+    score = O.h2o_score(q, k, lse, causal=True)
+    assert score.shape == case["score"].shape
+    assert (score - case["score"]).abs().max().item() <= 1e-5
+
+
 def test_gemm_epilogues_match_reference_capture(golden):
     gm = golden["gemm"]
     g = torch.Generator().manual_seed(gm["seed"])
