@@ -30,6 +30,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 
 namespace hb {
 
@@ -153,9 +154,11 @@ __device__ __forceinline__ void rowprog_run(const RowProgParams& p, int end, con
         for (int e = 0; e < kE; ++e) v[e] = x;
         break;
       }
-      default:  // HB_SRC_IMM, HB_SRC_NONE
+      case HB_SRC_IMM:
 #pragma unroll
         for (int e = 0; e < kE; ++e) v[e] = inst.imm;
+        break;
+      default:  // HB_SRC_NONE: unary ops, stores and reductions read no operand
         break;
     }
     // ---- operation (formulas: Heddle/heddle/frontend/codegen.py:1577-1609)
@@ -220,7 +223,7 @@ __device__ __forceinline__ void rowprog_run(const RowProgParams& p, int end, con
 // No reductions: a flat stream over the 16-byte groups of the matrix.
 template <typename T>
 __global__ void __launch_bounds__(kRpThreads) rowprog_stream_kernel(const __grid_constant__ RowProgParams p) {
-  __shared__ float tmp_s[HB_EW_MAX_TMP * kE * kRpThreads];
+  extern __shared__ float tmp_s[];  // [temporaries the program uses][kE][threads]
   const unsigned groups = static_cast<unsigned>(p.cols >> 3);
   const unsigned total = static_cast<unsigned>(p.rows) * groups;  // the host checks that this fits 32 bits
   const float red[4] = {0.f, 0.f, 0.f, 0.f};
@@ -257,7 +260,7 @@ __global__ void __launch_bounds__(kRpThreads) rowprog_reduce_kernel(const __grid
   constexpr int kThreadsPerRow = 32 * kWarpsPerRow;
   constexpr int kRowsPerCta = 4 / kWarpsPerRow;
   __shared__ float part[4];
-  __shared__ float tmp_s[HB_EW_MAX_TMP * kE * kRpThreads];
+  extern __shared__ float tmp_s[];  // [temporaries the program uses][kE][threads]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long row = kWarpsPerRow == 1 ? (blockIdx.x * static_cast<long long>(kRowsPerCta) + warp) : static_cast<long long>(blockIdx.x);
   const int t = kWarpsPerRow == 1 ? lane : static_cast<int>(threadIdx.x);
@@ -417,20 +420,40 @@ static int rowprog_impl(const hb_rowwise_args* a) {
   if (rc != HB_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   const bool bf16 = a->dtype == HB_BF16;
+  // dynamic shared memory: only the temporaries the program uses (16 KB each)
+  int n_tmp = 0;
+  for (int k = 0; k < HB_EW_MAX_TMP; ++k)
+    if (tmp_defined[k]) n_tmp = k + 1;
+  const size_t smem = (size_t)n_tmp * kE * kRpThreads * sizeof(float);
+  {
+    static std::mutex mu;
+    static bool configured[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    if (!configured[st->device & 63]) {
+      const int max_smem = HB_EW_MAX_TMP * kE * kRpThreads * (int)sizeof(float);
+      HB_CUDA_CHECK(cudaFuncSetAttribute(rowprog_stream_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+      HB_CUDA_CHECK(cudaFuncSetAttribute(rowprog_stream_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+      HB_CUDA_CHECK(cudaFuncSetAttribute(rowprog_reduce_kernel<__nv_bfloat16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+      HB_CUDA_CHECK(cudaFuncSetAttribute(rowprog_reduce_kernel<__half, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+      HB_CUDA_CHECK(cudaFuncSetAttribute(rowprog_reduce_kernel<__nv_bfloat16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+      HB_CUDA_CHECK(cudaFuncSetAttribute(rowprog_reduce_kernel<__half, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+      configured[st->device & 63] = true;
+    }
+  }
   if (p.n_red == 0) {
     const long long groups = a->rows * (a->cols / 8);
     const long long per_block = 1ll * kRpThreads * kG;
     const unsigned grid = static_cast<unsigned>(std::min<long long>((groups + per_block - 1) / per_block, 48ll * st->sm_count));
-    if (bf16) rowprog_stream_kernel<__nv_bfloat16><<<grid, kRpThreads, 0, stream>>>(p);
-    else rowprog_stream_kernel<__half><<<grid, kRpThreads, 0, stream>>>(p);
+    if (bf16) rowprog_stream_kernel<__nv_bfloat16><<<grid, kRpThreads, smem, stream>>>(p);
+    else rowprog_stream_kernel<__half><<<grid, kRpThreads, smem, stream>>>(p);
   } else if (a->cols <= 1024) {
     const unsigned grid = static_cast<unsigned>((a->rows + 3) / 4);
-    if (bf16) rowprog_reduce_kernel<__nv_bfloat16, 1><<<grid, 128, 0, stream>>>(p);
-    else rowprog_reduce_kernel<__half, 1><<<grid, 128, 0, stream>>>(p);
+    if (bf16) rowprog_reduce_kernel<__nv_bfloat16, 1><<<grid, 128, smem, stream>>>(p);
+    else rowprog_reduce_kernel<__half, 1><<<grid, 128, smem, stream>>>(p);
   } else {
     const unsigned grid = static_cast<unsigned>(a->rows);
-    if (bf16) rowprog_reduce_kernel<__nv_bfloat16, 4><<<grid, 128, 0, stream>>>(p);
-    else rowprog_reduce_kernel<__half, 4><<<grid, 128, 0, stream>>>(p);
+    if (bf16) rowprog_reduce_kernel<__nv_bfloat16, 4><<<grid, 128, smem, stream>>>(p);
+    else rowprog_reduce_kernel<__half, 4><<<grid, 128, smem, stream>>>(p);
   }
   HB_CUDA_CHECK(cudaGetLastError());
   return HB_OK;
