@@ -83,12 +83,16 @@ __device__ __forceinline__ uint4 rp_pack8(const float (&f)[8]) {
 // exp, reciprocal and friends through the MUFU: the results are rounded to 16 bits, for which the
 // approximate units (2 ulp of fp32) are exact enough, and an interpreter that has to stay under the
 // HBM roofline cannot afford the multi-instruction accurate versions.
-__device__ __forceinline__ float rp_exp(float x) { return __expf(x); }
-__device__ __forceinline__ float rp_rcp(float x) { return __fdividef(1.0f, x); }
-__device__ __forceinline__ float rp_sigmoid(float x) { return rp_rcp(1.0f + __expf(-x)); }
+__device__ __forceinline__ float rp_exp(float x) { return fast_exp2(x * 1.4426950408889634f); }
+__device__ __forceinline__ float rp_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rp_sigmoid(float x) { return rp_rcp(1.0f + fast_exp2(x * -1.4426950408889634f)); }
 __device__ __forceinline__ float rp_tanh(float x) {
   // 1 - 2 / (1 + exp(2x)); saturates correctly for large |x| (exp -> inf gives 1, exp -> 0 gives -1)
-  return 1.0f - 2.0f * rp_rcp(1.0f + __expf(2.0f * x));
+  return fmaf(-2.0f, rp_rcp(1.0f + fast_exp2(x * 2.8853900817779268f)), 1.0f);
 }
 
 // Register state of the machine: kG groups of 8 columns are interpreted together, so that one
@@ -172,16 +176,16 @@ __device__ __forceinline__ void rowprog_run(const RowProgParams& p, int end, con
       case HB_EW_SUB: HB_RP_EACH(a[e] - v[e]);
       case HB_EW_RSUB: HB_RP_EACH(v[e] - a[e]);
       case HB_EW_MUL: HB_RP_EACH(a[e] * v[e]);
-      case HB_EW_DIV: HB_RP_EACH(__fdividef(a[e], v[e]));
-      case HB_EW_RDIV: HB_RP_EACH(__fdividef(v[e], a[e]));
+      case HB_EW_DIV: HB_RP_EACH(a[e] * rp_rcp(v[e]));
+      case HB_EW_RDIV: HB_RP_EACH(v[e] * rp_rcp(a[e]));
       case HB_EW_MAX: HB_RP_EACH(fmaxf(a[e], v[e]));
       case HB_EW_MIN: HB_RP_EACH(fminf(a[e], v[e]));
       case HB_EW_POW: HB_RP_EACH(powf(a[e], v[e]));
       case HB_EW_NEG: HB_RP_EACH(-a[e]);
       case HB_EW_ABS: HB_RP_EACH(fabsf(a[e]));
       case HB_EW_EXP: HB_RP_EACH(rp_exp(a[e]));
-      case HB_EW_LOG: HB_RP_EACH(__logf(a[e]));
-      case HB_EW_LOG2: HB_RP_EACH(__log2f(a[e]));
+      case HB_EW_LOG: HB_RP_EACH(fast_log2(a[e]) * 0.6931471805599453f);
+      case HB_EW_LOG2: HB_RP_EACH(fast_log2(a[e]));
       case HB_EW_SQRT: HB_RP_EACH(sqrtf(a[e]));
       case HB_EW_RSQRT: HB_RP_EACH(rsqrtf(a[e]));
       case HB_EW_RECIP: HB_RP_EACH(rp_rcp(a[e]));

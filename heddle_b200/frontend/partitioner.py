@@ -328,20 +328,19 @@ class LoweredPartition:
 
 
 def lower_partition(p: Partition, support: Optional[SupportPolicy] = None,
-                    exact_intermediates: Optional[bool] = None) -> Optional[LoweredPartition]:
+                    exact_intermediates: bool = False) -> Optional[LoweredPartition]:
     """Linearise a group into an accumulator-machine program, or None when it does not fit the
     machine (too many live values, operands or instructions).
 
     Every node becomes ``acc = op(acc, operand)``; a value that is still needed when acc is about to
-    be overwritten is saved to a temporary first.  With ``exact_intermediates`` acc is rounded to the
-    16-bit type after each node whose eager result is a 16-bit tensor, so the fused result equals
-    eager arithmetic up to the difference between the fp32 formulas (the reference computes its
-    pointwise chains in the buffers' own 16-bit type, codegen.py:1466-1490).  The default is on for
-    pure pointwise groups and off for groups with reductions, which then run entirely in fp32 with
-    fp32 reduction results, as the reference's reduction kernel does (codegen.py:1438-1440)."""
+    be overwritten is saved to a temporary first.  The chain runs in fp32 and is rounded once, when it
+    is stored: that is the arithmetic of the path's oracle (the FX graph executed eagerly in fp32) and of
+    the reference's reduction kernel, which keeps its intermediate and reduction results in fp32
+    (codegen.py:1438-1440).  With ``exact_intermediates`` acc is instead rounded to the 16-bit type after
+    every node whose eager result is a 16-bit tensor, which reproduces eager 16-bit PyTorch (and the
+    reference's pointwise kernels, which compute in the buffers' own type, codegen.py:1466-1490) up to
+    the last bits of the fp32 formulas."""
     support = support or SupportPolicy.default()
-    if exact_intermediates is None:
-        exact_intermediates = not any(support.family(n) == "reduction" for n in p.nodes)
     node_set = set(p.nodes)
     full, dtype = p.shape, p.dtype
     inputs: List[fx.Node] = []

@@ -39,38 +39,61 @@ class Recorder(fx.Interpreter):
         return out
 
 
+def eval_partition_fp32(p, values):
+    """The partition's nodes evaluated in fp32 from the graph's own (16-bit valued) partition inputs."""
+    env = {}
+
+    def val(a):
+        if isinstance(a, fx.Node):
+            if a in env:
+                return env[a]
+            v = values[a]
+            return v.float() if isinstance(v, torch.Tensor) and v.is_floating_point() else v
+        return a
+
+    for n in p.nodes:
+        args = fx.node.map_arg(n.args, val)
+        kwargs = fx.node.map_arg(n.kwargs, val)
+        env[n] = n.target(*args, **kwargs) if n.op == "call_function" else getattr(args[0], n.target)(*args[1:], **kwargs)
+    return env
+
+
 def check_partitions(module, *inputs, expect_parts=None, tol_ulps=2.0, **env):
-    """Partition + lower the captured graph; every program must reproduce the graph's own values."""
+    """Partition + lower the captured graph; every program must reproduce the graph's own values: the
+    fp32 evaluation of the graph for the default lowering (fp32 chain, one rounding at the store), and
+    the 16-bit eager evaluation for ``exact_intermediates=True`` on pure pointwise groups."""
     gm = capture_raw(module, *inputs)
     gp = GraphPartitioner(gm)
     parts = gp.partition()
     if expect_parts is not None:
         assert len(parts) == expect_parts, (gp.prune_stats, [[n.name for n in p.nodes] for p in parts])
     rec = Recorder(gm)
-    rec32 = Recorder(gm)  # the same graph evaluated in fp32 on the same (16-bit valued) inputs
     with torch.no_grad():
         rec.run(*inputs)
-        rec32.run(*[t.float() if isinstance(t, torch.Tensor) else t for t in inputs])
     lowered = []
     for p in parts:
-        lp = lower_partition(p)
-        assert lp is not None, [n.name for n in p.nodes]
-        outs = run_program(lp.program, [rec.values[n] for n in lp.inputs], [rec.values[n] for n in lp.rowvecs],
-                           [rec.values[n] for n in lp.rowscalars], len(lp.outputs))
-        outs = outs if isinstance(outs, tuple) else (outs,)
-        has_reduction = any(i[0].startswith("reduce_") for i in lp.program)
-        for node, got in zip(lp.outputs, outs):
-            # pointwise groups reproduce eager's 16-bit intermediates; groups with reductions run in fp32
-            # throughout (as the reference's reduction kernel), so they are compared with the fp32 graph
-            want = rec32.values[node].to(rec.values[node].dtype) if has_reduction else rec.values[node]
-            assert got.shape == want.shape and got.dtype == want.dtype
-            # eager rounds every intermediate to 16 bit as the program does (HB_EW_ROUND); what is left
-            # is the difference between two fp32 evaluations of the same formula: a few 16-bit ulps
-            eps = 2.0 ** -8 if want.dtype == torch.bfloat16 else 2.0 ** -11
-            err = (got.float() - want.float()).abs()
-            bound = tol_ulps * eps * want.float().abs().clamp_min(1e-3) + 1e-6
-            assert bool((err <= bound).all()), (node.name, float(err.max()), lp.program)
-        lowered.append(lp)
+        has_reduction = any(n.target in (torch.sum, torch.mean, torch.amax) or str(n.target) in ("sum", "mean", "amax")
+                            for n in p.nodes)
+        modes = (False,) if has_reduction else (False, True)
+        with torch.no_grad():
+            fp32 = eval_partition_fp32(p, rec.values)
+        for exact in modes:
+            lp = lower_partition(p, exact_intermediates=exact)
+            assert lp is not None, [n.name for n in p.nodes]
+            assert any(i[0] == "round" for i in lp.program) == exact
+            outs = run_program(lp.program, [rec.values[n] for n in lp.inputs], [rec.values[n] for n in lp.rowvecs],
+                               [rec.values[n] for n in lp.rowscalars], len(lp.outputs))
+            outs = outs if isinstance(outs, tuple) else (outs,)
+            for node, got in zip(lp.outputs, outs):
+                # default: the fp32 graph rounded once; exact: eager's own 16-bit values.  What is left is the
+                # difference between two fp32 evaluations of the same formula: a few 16-bit ulps
+                want = rec.values[node] if exact else fp32[node].to(rec.values[node].dtype)
+                assert got.shape == want.shape and got.dtype == want.dtype
+                eps = 2.0 ** -8 if want.dtype == torch.bfloat16 else 2.0 ** -11
+                err = (got.float() - want.float()).abs()
+                bound = tol_ulps * eps * want.float().abs().clamp_min(1e-3) + 1e-6
+                assert bool((err <= bound).all()), (node.name, exact, float(err.max()), lp.program)
+        lowered.append(lower_partition(p))
     return gm, parts, lowered
 
 
