@@ -65,7 +65,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     (OBJ_DIR / "ptxas.log").write_text(log)
     if verbose:
         sys.stderr.write(log)
-    cmd = [_nvcc(), "-shared", "-cudart", "static", "-o", str(LIB_PATH), *[str(o) for o, _ in results]]
+    cmd = [_nvcc(), "-shared", "-cudart", "static", "-o", str(LIB_PATH), *[str(o) for o, _ in results], "-ldl"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")

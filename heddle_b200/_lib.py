@@ -130,13 +130,16 @@ class RowwiseArgs(C.Structure):
         ("outputs", C.c_void_p * EW_MAX_OUTPUTS), ("ld_out", C.c_int64 * EW_MAX_OUTPUTS),
         ("n_inputs", C.c_int32), ("n_rowvec", C.c_int32), ("n_rowscalar", C.c_int32), ("n_outputs", C.c_int32),
         ("rows", C.c_int64), ("cols", C.c_int32), ("dtype", C.c_int32), ("n_inst", C.c_int32),
-        ("program", EwInst * EW_MAX_INST), ("stream", C.c_void_p),
+        ("program", EwInst * EW_MAX_INST), ("stream", C.c_void_p), ("mode", C.c_int32),
     ]
+
+
+ROWWISE_AUTO, ROWWISE_INTERPRET, ROWWISE_COMPILED = 0, 1, 2
 
 
 # every symbol include/heddle_b200.h declares
 EXPORTS = (
-    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_status_word_noalloc", "hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_rowwise_program", "hb_status_word",
+    "hb_fa_fwd", "hb_fa_fwd_noalloc", "hb_status_word_noalloc", "hb_fa_bwd_preprocess", "hb_fa_bwd_dkdv", "hb_fa_bwd_dq", "hb_h2o_score", "hb_gemm_epilogue", "hb_rms_rowstat", "hb_prepare_weight", "hb_row_softmax", "hb_rowwise_program", "hb_rowwise_compiler_available", "hb_debug_rowwise_compile", "hb_status_word",
     "hb_version",
     "hb_query", "hb_last_error", "hb_shutdown", "hb_debug_umma", "hb_debug_wait_timeout", "hb_debug_fa_fwd_stages",
 )
@@ -176,6 +179,10 @@ def load() -> C.CDLL:
     lib.hb_row_softmax.restype = C.c_int
     lib.hb_rowwise_program.argtypes = [C.POINTER(RowwiseArgs)]
     lib.hb_rowwise_program.restype = C.c_int
+    lib.hb_rowwise_compiler_available.argtypes = []
+    lib.hb_rowwise_compiler_available.restype = C.c_int
+    lib.hb_debug_rowwise_compile.argtypes = [C.POINTER(RowwiseArgs), C.c_char_p, C.c_int64]
+    lib.hb_debug_rowwise_compile.restype = C.c_int
     lib.hb_status_word.argtypes = [C.POINTER(C.c_uint32)]
     lib.hb_status_word.restype = C.c_int
     lib.hb_status_word_noalloc.argtypes = [C.POINTER(C.c_uint32), C.c_void_p]

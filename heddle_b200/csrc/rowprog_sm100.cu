@@ -5,8 +5,10 @@
 // pointwise chains (Heddle/heddle/frontend/codegen.py:1457-1498, op table _map_op :1577-1609) and
 // softmax-like / sum / mean / max reductions over the last axis (:1246-1455: one pass per reduction
 // that recomputes the expression up to it, results kept in fp32, then an output pass).  Here the
-// FX lowering linearises the same partition into an accumulator-machine program that one
-// precompiled kernel interprets: nothing is compiled at run time.
+// FX lowering linearises the same partition into an accumulator-machine program.  This file holds
+// the argument checks and the precompiled kernels that INTERPRET such a program (used when the
+// caller asks for it or when NVRTC cannot be loaded); rowprog_jit.cu turns the same program into a
+// kernel specialised for it, which is the default path.
 //
 // Machine, per group of 8 consecutive columns of a row (16 bytes of a 16-bit tensor):
 //   acc[8]           the running value (fp32), in registers
@@ -27,27 +29,13 @@
 // intermediate tensors of the eager graph; the lowering decides where it is needed.
 #include "host_common.h"
 #include "ptx_sm100.cuh"
+#include "rowprog_sm100.cuh"
 
 #include <algorithm>
 #include <cstring>
 #include <mutex>
 
 namespace hb {
-
-struct alignas(16) RowProgParams {
-  const void* in[HB_EW_MAX_INPUTS];
-  long long ld_in[HB_EW_MAX_INPUTS];
-  const void* rowvec[HB_EW_MAX_ROWVEC];
-  const float* rowscalar[HB_EW_MAX_ROWSCALAR];
-  void* out[HB_EW_MAX_OUTPUTS];
-  long long ld_out[HB_EW_MAX_OUTPUTS];
-  long long rows;
-  int cols;
-  int n_inst;
-  int n_red;
-  int red_pc[HB_EW_MAX_RED];  // position of the r-th reduction instruction
-  hb_ew_inst prog[HB_EW_MAX_INST];
-};
 
 template <typename T>
 __device__ __forceinline__ void rp_unpack8(const uint4& w, float (&f)[8]);
@@ -328,7 +316,9 @@ __global__ void __launch_bounds__(kRpThreads) rowprog_reduce_kernel(const __grid
 
 static bool rp_aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
-static int rowprog_impl(const hb_rowwise_args* a) {
+// Checks the arguments and the program and fills the kernel parameters; *n_tmp receives the number
+// of temporaries the program uses.
+static int rowprog_validate(const hb_rowwise_args* a, RowProgParams& p, int* n_tmp) {
   if (a == nullptr) return set_error(HB_ERR_BAD_ARG, "hb_rowwise_program: args is NULL");
   if (a->rows < 0 || a->cols <= 0) return set_error(HB_ERR_BAD_ARG, "hb_rowwise_program: negative or zero extent");
   if (a->dtype != HB_BF16 && a->dtype != HB_FP16)
@@ -339,10 +329,11 @@ static int rowprog_impl(const hb_rowwise_args* a) {
   if (a->n_inputs < 0 || a->n_inputs > HB_EW_MAX_INPUTS || a->n_rowvec < 0 || a->n_rowvec > HB_EW_MAX_ROWVEC ||
       a->n_rowscalar < 0 || a->n_rowscalar > HB_EW_MAX_ROWSCALAR || a->n_outputs < 1 || a->n_outputs > HB_EW_MAX_OUTPUTS)
     return set_error(HB_ERR_BAD_ARG, "hb_rowwise_program: operand counts out of range");
+  if (a->mode < HB_ROWWISE_AUTO || a->mode > HB_ROWWISE_COMPILED)
+    return set_error(HB_ERR_BAD_ARG, "hb_rowwise_program: unknown mode %d", a->mode);
   if (a->n_inst < 1 || a->n_inst > HB_EW_MAX_INST)
     return set_error(HB_ERR_BAD_ARG, "hb_rowwise_program: program length %d not in 1..%d", a->n_inst, HB_EW_MAX_INST);
 
-  RowProgParams p;
   memset(&p, 0, sizeof(p));
   for (int i = 0; i < a->n_inputs; ++i) {
     if (a->inputs[i] == nullptr || !rp_aligned16(a->inputs[i]) || a->ld_in[i] < a->cols || a->ld_in[i] % 8 != 0)
@@ -414,20 +405,35 @@ static int rowprog_impl(const hb_rowwise_args* a) {
   }
   for (int i = 0; i < a->n_outputs; ++i)
     if (!stored[i]) return set_error(HB_ERR_BAD_ARG, "hb_rowwise_program: output %d is never stored", i);
-  if (a->rows == 0) return HB_OK;
   p.rows = a->rows;
   p.cols = a->cols;
   p.n_inst = a->n_inst;
+  *n_tmp = 0;
+  for (int k = 0; k < HB_EW_MAX_TMP; ++k)
+    if (tmp_defined[k]) *n_tmp = k + 1;
+  return HB_OK;
+}
+
+static int rowprog_impl(const hb_rowwise_args* a) {
+  RowProgParams p;
+  int n_tmp = 0;
+  const int vrc = rowprog_validate(a, p, &n_tmp);
+  if (vrc != HB_OK) return vrc;
+  if (a->rows == 0) return HB_OK;
 
   DeviceState* st = nullptr;
   const int rc = get_device_state(&st);
   if (rc != HB_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   const bool bf16 = a->dtype == HB_BF16;
+  if (a->mode != HB_ROWWISE_INTERPRET) {
+    const int jit = rowprog_jit_launch(p, bf16, *st, stream);
+    if (jit == kJitLaunched) return HB_OK;
+    if (jit == kJitError) return HB_ERR_CUDA;  // the message is set
+    if (a->mode == HB_ROWWISE_COMPILED)
+      return set_error(HB_ERR_UNSUPPORTED, "hb_rowwise_program: the run-time compiler (libnvrtc) cannot be loaded in this process");
+  }
   // dynamic shared memory: only the temporaries the program uses (16 KB each)
-  int n_tmp = 0;
-  for (int k = 0; k < HB_EW_MAX_TMP; ++k)
-    if (tmp_defined[k]) n_tmp = k + 1;
   const size_t smem = (size_t)n_tmp * kE * kRpThreads * sizeof(float);
   {
     static std::mutex mu;
@@ -464,6 +470,17 @@ static int rowprog_impl(const hb_rowwise_args* a) {
 }
 
 }  // namespace hb
+
+extern "C" int hb_rowwise_compiler_available(void) { return hb::rowprog_jit_available(); }
+
+extern "C" int hb_debug_rowwise_compile(const hb_rowwise_args* args, char* source, int64_t capacity) {
+  hb::clear_error();
+  hb::RowProgParams p;
+  int n_tmp = 0;
+  const int rc = hb::rowprog_validate(args, p, &n_tmp);
+  if (rc != HB_OK) return rc;
+  return hb::rowprog_jit_compile_only(p, args->dtype == HB_BF16, source, capacity);
+}
 
 extern "C" int hb_rowwise_program(const hb_rowwise_args* args) {
   hb::clear_error();

@@ -435,14 +435,15 @@ def row_softmax(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     return y.reshape(x.shape)
 
 
-def rowwise_program(program, inputs=(), rowvecs=(), rowscalars=(), n_outputs: int = 1):
+def rowwise_program(program, inputs=(), rowvecs=(), rowscalars=(), n_outputs: int = 1, mode: str = "auto"):
     """Run an accumulator-machine program over [rows, cols] views of ``inputs`` (``hb_rowwise_program``).
 
     ``program`` is a sequence of ``(op, src, index, imm)`` tuples with the names of ``_lib.EW_OPS`` /
     ``_lib.EW_SRCS`` (``src`` may be None for unary ops).  ``inputs`` are 16-bit tensors of one shape
     (..., cols); ``rowvecs`` are [cols] vectors; ``rowscalars`` are tensors with one value per row
     (shape (..., 1) or (...)), converted to fp32.  Returns ``n_outputs`` new tensors shaped like the
-    inputs (a tuple when ``n_outputs`` > 1)."""
+    inputs (a tuple when ``n_outputs`` > 1).  ``mode``: "auto" (a kernel compiled for this program at
+    run time and cached; the interpreter kernel where NVRTC cannot be loaded), "interpret" or "compiled"."""
     if not inputs:
         raise ValueError("rowwise_program needs at least one full-size input")
     _require_cuda(*inputs, *rowvecs, *rowscalars)
@@ -488,6 +489,7 @@ def rowwise_program(program, inputs=(), rowvecs=(), rowscalars=(), n_outputs: in
         a.program[pc].index = int(index)
         a.program[pc].imm = float(imm)
     a.stream = _stream_ptr(x0.device)
+    a.mode = {"auto": _lib.ROWWISE_AUTO, "interpret": _lib.ROWWISE_INTERPRET, "compiled": _lib.ROWWISE_COMPILED}[mode]
     with torch.cuda.device(x0.device):
         _lib.check(_lib.load().hb_rowwise_program(C.byref(a)))
     return outs[0] if n_outputs == 1 else tuple(outs)

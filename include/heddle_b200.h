@@ -397,9 +397,24 @@ typedef struct hb_rowwise_args {
   int32_t n_inst;
   hb_ew_inst program[HB_EW_MAX_INST];
   void* stream;
+  int32_t mode; /* hb_rowwise_mode */
 } hb_rowwise_args;
 
+/* How the program is executed.  AUTO: a kernel specialised for the program, compiled at run time
+ * with NVRTC on its first use and cached (the reference compiles its generated kernels the same
+ * way); when libnvrtc cannot be loaded, the interpreter kernel.  INTERPRET: always the interpreter
+ * (nothing is compiled).  COMPILED: the specialised kernel or HB_ERR_UNSUPPORTED.  All three give
+ * the same results.  HEDDLE_B200_ROWWISE_JIT=0 in the environment turns the compiler off;
+ * HEDDLE_B200_NVRTC names the library file to load. */
+typedef enum hb_rowwise_mode { HB_ROWWISE_AUTO = 0, HB_ROWWISE_INTERPRET = 1, HB_ROWWISE_COMPILED = 2 } hb_rowwise_mode;
+
 int hb_rowwise_program(const hb_rowwise_args* args);
+/* 1 when the run-time compiler can be loaded in this process, else 0.  Needs no device. */
+int hb_rowwise_compiler_available(void);
+/* Test hook: checks `args` like hb_rowwise_program, generates the specialised kernel's source and
+ * compiles it for sm_100a without loading or launching it (no device is needed and no pointer in
+ * `args` is dereferenced).  `source` (may be NULL) receives the generated text. */
+int hb_debug_rowwise_compile(const hb_rowwise_args* args, char* source, int64_t capacity);
 
 /* Device-side status word of the current device (0 = no bounded wait ever gave up);
  * reading it synchronises the device.  *out always receives the word; the return value is

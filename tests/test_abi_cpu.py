@@ -50,8 +50,9 @@ int main(void) {
   printf("%zu %zu %zu %zu %zu\n", sizeof(hb_fa_bwd_args), offsetof(hb_fa_bwd_args, B), offsetof(hb_fa_bwd_args, q_stride_b),
          offsetof(hb_fa_bwd_args, causal), offsetof(hb_fa_bwd_args, stream));
   printf("%zu %zu %zu\n", offsetof(hb_gemm_args, batch), offsetof(hb_gemm_args, w_layout), offsetof(hb_gemm_args, r_batch_stride));
-  printf("%zu %zu %zu %zu %zu %zu\n", sizeof(hb_rowwise_args), offsetof(hb_rowwise_args, rowscalar), offsetof(hb_rowwise_args, n_inputs),
-         offsetof(hb_rowwise_args, rows), offsetof(hb_rowwise_args, program), offsetof(hb_rowwise_args, stream));
+  printf("%zu %zu %zu %zu %zu %zu %zu\n", sizeof(hb_rowwise_args), offsetof(hb_rowwise_args, rowscalar), offsetof(hb_rowwise_args, n_inputs),
+         offsetof(hb_rowwise_args, rows), offsetof(hb_rowwise_args, program), offsetof(hb_rowwise_args, stream),
+         offsetof(hb_rowwise_args, mode));
   return 0;
 }'''
     with tempfile.TemporaryDirectory() as d:
@@ -77,7 +78,8 @@ int main(void) {
     assert gb == [_lib.GemmArgs.batch.offset, _lib.GemmArgs.w_layout.offset, _lib.GemmArgs.r_batch_stride.offset]
     rw = [int(x) for x in lines[6].split()]
     assert rw == [ctypes.sizeof(_lib.RowwiseArgs), _lib.RowwiseArgs.rowscalar.offset, _lib.RowwiseArgs.n_inputs.offset,
-                  _lib.RowwiseArgs.rows.offset, _lib.RowwiseArgs.program.offset, _lib.RowwiseArgs.stream.offset]
+                  _lib.RowwiseArgs.rows.offset, _lib.RowwiseArgs.program.offset, _lib.RowwiseArgs.stream.offset,
+                  _lib.RowwiseArgs.mode.offset]
     assert ctypes.sizeof(_lib.EwInst) == 16
 
 
@@ -145,6 +147,58 @@ def test_argument_validation_needs_no_gpu(built_lib):
     r.program[1].op, r.program[1].src, r.program[1].index = _lib.EW_OPS["add"], _lib.EW_SRCS["tmp"], 1
     assert built_lib.hb_rowwise_program(ctypes.byref(r)) == _lib.HB_ERR_BAD_ARG
     assert b"before it is stored" in built_lib.hb_last_error()
+    r.mode = 7
+    assert built_lib.hb_rowwise_program(ctypes.byref(r)) == _lib.HB_ERR_BAD_ARG
+    assert b"unknown mode" in built_lib.hb_last_error()
+
+
+def _rowwise_args(program, cols=4096, dtype=None, n_in=2, n_vec=1, n_sc=1, n_out=1):
+    """Arguments with aligned placeholder addresses: the compile-only hook never dereferences them."""
+    from heddle_b200 import _lib
+    a = _lib.RowwiseArgs()
+    for i in range(n_in):
+        a.inputs[i], a.ld_in[i] = 0x10000, cols
+    for i in range(n_vec):
+        a.rowvec[i] = 0x10000
+    for i in range(n_sc):
+        a.rowscalar[i] = 0x10000
+    for i in range(n_out):
+        a.outputs[i], a.ld_out[i] = 0x10000, cols
+    a.n_inputs, a.n_rowvec, a.n_rowscalar, a.n_outputs = n_in, n_vec, n_sc, n_out
+    a.rows, a.cols, a.dtype, a.n_inst = 128, cols, _lib.HB_BF16 if dtype is None else dtype, len(program)
+    for pc, (op, src, idx, imm) in enumerate(program):
+        a.program[pc].op, a.program[pc].src = _lib.EW_OPS[op], _lib.EW_SRCS[src or "none"]
+        a.program[pc].index, a.program[pc].imm = idx, imm
+    return a
+
+
+def test_every_program_shape_compiles_for_sm100a_without_a_gpu(built_lib):
+    """The run-time specialised rowwise kernels: source generation + NVRTC for sm_100a need no device."""
+    from heddle_b200 import _lib
+    if not built_lib.hb_rowwise_compiler_available():
+        pytest.skip("libnvrtc cannot be loaded in this process")
+    unary = [k for k, v in _lib.EW_OPS.items() if 16 <= v <= 30]
+    binary = [k for k, v in _lib.EW_OPS.items() if 1 <= v <= 9]
+    prog = [("load", "input", 0, 0.0)] + [(u, None, 0, 0.0) for u in unary] + [("store_tmp", None, 1, 0.0)]
+    srcs = [("input", 1), ("rowvec", 0), ("rowscalar", 0), ("imm", 0), ("tmp", 1)]
+    prog += [(b,) + srcs[i % 5] + (float("inf") if i == 3 else 1.5,) for i, b in enumerate(binary)]
+    prog.append(("store_out", None, 0, 0.0))
+    text = ctypes.create_string_buffer(1 << 16)
+    for dtype in (_lib.HB_BF16, _lib.HB_FP16):
+        rc = built_lib.hb_debug_rowwise_compile(ctypes.byref(_rowwise_args(prog, dtype=dtype)), text, len(text))
+        assert rc == _lib.HB_OK, built_lib.hb_last_error()
+    src = text.value.decode()
+    assert src.count("EACH(") >= len(unary) + len(binary) and "0x7f800000" in src  # the infinite immediate, bit-exact
+    softmax = [("load", "input", 0, 0.0), ("reduce_max", None, 0, 0.0), ("sub", "reduced", 0, 0.0), ("exp", None, 0, 0.0),
+               ("store_tmp", None, 0, 0.0), ("reduce_sum", None, 1, 0.0), ("load", "tmp", 0, 0.0), ("div", "reduced", 1, 0.0),
+               ("store_out", None, 0, 0.0)]
+    for cols in (512, 4096):  # one warp per row / one CTA per row
+        rc = built_lib.hb_debug_rowwise_compile(ctypes.byref(_rowwise_args(softmax, cols=cols)), text, len(text))
+        assert rc == _lib.HB_OK, built_lib.hb_last_error()
+        assert f"#define HB_WARPS_PER_ROW {1 if cols <= 1024 else 4}" in text.value.decode()
+    # the hook validates like the entry point
+    bad = _rowwise_args([("exp", None, 0, 0.0), ("store_out", None, 0, 0.0)])
+    assert built_lib.hb_debug_rowwise_compile(ctypes.byref(bad), None, 0) == _lib.HB_ERR_BAD_ARG
 
 
 def test_ops_reject_cpu_tensors(built_lib):

@@ -11,10 +11,26 @@ from oracle.program_oracle import run_program
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def ops(built_lib):
+class _OpsInMode:
+    """The package's ops with ``rowwise_program`` pinned to one execution mode."""
+
+    def __init__(self, ops, mode):
+        self._ops, self.mode = ops, mode
+
+    def rowwise_program(self, *args, **kw):
+        return self._ops.rowwise_program(*args, mode=self.mode, **kw)
+
+    def __getattr__(self, name):
+        return getattr(self._ops, name)
+
+
+@pytest.fixture(scope="module", params=["compiled", "interpret"])
+def ops(built_lib, request):
+    """Every test runs on the kernel compiled for its program and on the interpreter kernel."""
     from heddle_b200 import ops as _ops
-    return _ops
+    if request.param == "compiled" and not built_lib.hb_rowwise_compiler_available():
+        pytest.fail("libnvrtc cannot be loaded on this machine: the specialised rowwise kernels cannot run")
+    return _OpsInMode(_ops, request.param)
 
 
 def _t(*shape, seed=0, dtype=torch.bfloat16, scale=1.0):
