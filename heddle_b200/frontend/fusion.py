@@ -168,6 +168,69 @@ def hb_matmul(a, b):
     return out.reshape(*lead, a.shape[-2], b.shape[-1])
 
 
+def einsum_plan(equation: str, shape_a, shape_b):
+    """Reads a two-operand einsum as a batched GEMM: labels in both operands and the output are the
+    batch, labels in both operands only are contracted, the rest are the free (M / N) labels of the
+    operand they occur in — the classification of the reference's ND-GEMM generator
+    (Heddle/heddle/frontend/codegen.py:455-470).  Returns None for what is not such a product
+    (ellipsis, implicit output, repeated labels, a label summed out of one operand, nothing contracted)."""
+    eq = equation.replace(" ", "")
+    if "->" not in eq or "." in eq:
+        return None
+    lhs, out = eq.split("->")
+    if lhs.count(",") != 1:
+        return None
+    ia, ib = lhs.split(",")
+    if len(set(ia)) != len(ia) or len(set(ib)) != len(ib) or len(set(out)) != len(out):
+        return None
+    if len(ia) != len(shape_a) or len(ib) != len(shape_b) or not set(out) <= set(ia) | set(ib):
+        return None
+    size = {}
+    for labels, shape in ((ia, shape_a), (ib, shape_b)):
+        for c, n in zip(labels, shape):
+            if size.setdefault(c, int(n)) != int(n):
+                return None  # broadcasting of size-1 dimensions stays in PyTorch
+    batch = [c for c in out if c in ia and c in ib]
+    contracted = [c for c in ia if c in ib and c not in out]
+    a_free = [c for c in ia if c not in ib]
+    b_free = [c for c in ib if c not in ia]
+    if not contracted or any(c not in out for c in a_free + b_free):
+        return None
+
+    def prod(labels):
+        r = 1
+        for c in labels:
+            r *= size[c]
+        return r
+
+    return {"ia": ia, "ib": ib, "out": out, "batch": batch, "contracted": contracted, "a_free": a_free, "b_free": b_free,
+            "size": size, "B": prod(batch), "M": prod(a_free), "N": prod(b_free), "K": prod(contracted)}
+
+
+@torch.fx.wrap
+def hb_einsum(equation, a, b):
+    """Two-operand ``torch.einsum`` as ONE launch of the batched tcgen05 GEMM: the operands are viewed
+    as [batch, M, K] and [batch, K, N] (permutations are views; a copy is made only where the merged
+    dimensions are not contiguous in storage), the right operand keeps whichever of its two layouts
+    it already has, and the result is viewed back in the output's label order.  The reference
+    generates an ND-indexed GEMM for the same node (Heddle/heddle/frontend/codegen.py:412-978)."""
+    plan = einsum_plan(equation, a.shape, b.shape)
+    if plan is None:
+        raise ValueError(f"hb_einsum cannot read {equation!r} as a batched matrix product")
+    ia, ib, size = plan["ia"], plan["ib"], plan["size"]
+    batch, con, af, bf = plan["batch"], plan["contracted"], plan["a_free"], plan["b_free"]
+    a3 = a.permute([ia.index(c) for c in batch + af + con]).reshape(plan["B"], plan["M"], plan["K"])
+    # contracted labels last in b's own order: [batch, N, K] storage, read through the K-major path
+    if [c for c in ib if c not in batch][-len(con):] == con:
+        b3 = b.permute([ib.index(c) for c in batch + bf + con]).reshape(plan["B"], plan["N"], plan["K"]).transpose(1, 2)
+    else:
+        b3 = b.permute([ib.index(c) for c in batch + con + bf]).reshape(plan["B"], plan["K"], plan["N"])
+    o3 = ops.bmm(a3, b3)
+    natural = batch + af + bf
+    o = o3.reshape([size[c] for c in natural])
+    return o.permute([natural.index(c) for c in plan["out"]])
+
+
 @torch.fx.wrap
 def hb_rowwise(inputs, rowvecs, rowscalars, program, n_outputs=1):
     """A fused group of pointwise / row-reduction nodes as one ``hb_rowwise_program`` launch.
@@ -581,6 +644,33 @@ def _pass_matmul(gm: fx.GraphModule) -> int:
     return done
 
 
+def _pass_einsum(gm: fx.GraphModule) -> int:
+    """Two-operand ``torch.einsum`` of 16-bit tensors that reads as a batched product -> ``hb_einsum``."""
+    done = 0
+    for n in list(gm.graph.nodes):
+        if n.op != "call_function" or _fname(n) != "einsum" or n.kwargs:
+            continue
+        args = list(n.args)
+        if len(args) == 2 and isinstance(args[1], (list, tuple)):
+            args = [args[0], *args[1]]
+        if len(args) != 3 or not isinstance(args[0], str) or not all(isinstance(t, fx.Node) for t in args[1:]):
+            continue
+        a, b = args[1], args[2]
+        sa, sb = _meta_shape(a), _meta_shape(b)
+        if sa is None or sb is None or _meta_dtype(a) not in (torch.bfloat16, torch.float16) or _meta_dtype(b) != _meta_dtype(a):
+            continue
+        plan = einsum_plan(args[0], sa, sb)
+        if plan is None or plan["K"] % 8 or plan["N"] % 8 or 0 in (plan["B"], plan["M"]):
+            continue
+        with gm.graph.inserting_before(n):
+            new = gm.graph.call_function(hb_einsum, (args[0], a, b))
+        new.meta = dict(n.meta)
+        n.replace_all_uses_with(new)
+        gm.graph.erase_node(n)
+        done += 1
+    return done
+
+
 def _softmax_dim(n: fx.Node):
     """(input, dim, has_dtype) of a softmax node, or None."""
     name = _fname(n)
@@ -681,6 +771,7 @@ def fuse_gemm_epilogues(gm: fx.GraphModule) -> int:
     _pass_rope(gm)
     _pass_merge_siblings(gm)
     _pass_matmul(gm)
+    _pass_einsum(gm)
     _pass_softmax(gm)
     _pass_rowwise(gm)
     gm.graph.lint()

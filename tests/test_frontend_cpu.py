@@ -342,3 +342,42 @@ def test_leftover_softmax_is_lowered_with_its_scale():
     leaves = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is fusion.hb_softmax]
     # only the last-axis, 16-bit one is taken (with its 1/4 folded); dim=1 and fp32 stay in PyTorch
     assert len(leaves) == 1 and leaves[0].args[1] == 0.25
+
+
+def test_einsum_is_read_as_a_batched_product():
+    """Two-operand einsums become hb_einsum when they are batched matrix products (the reference's
+    ND-GEMM generator takes the same class, codegen.py:412-470); the plan is checked on CPU by
+    replaying it with torch.bmm."""
+    cases = [("bhid,bhjd->bhij", (2, 3, 16, 32), (2, 3, 24, 32)),      # QK^T: contracted last in both
+             ("bhij,bhjd->bhid", (2, 3, 16, 24), (2, 3, 24, 32)),      # PV: row-major right operand
+             ("bld,dn->bln", (2, 16, 32), (32, 40)),                   # no batch label: one product
+             ("bnl,bdl->bnd", (2, 8, 16), (2, 24, 16)),
+             ("ibk,kjb->bji", (5, 2, 16), (16, 8, 2))]                 # permuted output, batch in the middle
+    for eq, sa, sb in cases:
+        g = torch.Generator().manual_seed(len(eq))
+        a, b = torch.randn(*sa, generator=g), torch.randn(*sb, generator=g)
+        plan = fusion.einsum_plan(eq, sa, sb)
+        assert plan is not None, eq
+        ia, ib = plan["ia"], plan["ib"]
+        batch, con, af, bf = plan["batch"], plan["contracted"], plan["a_free"], plan["b_free"]
+        a3 = a.permute([ia.index(c) for c in batch + af + con]).reshape(plan["B"], plan["M"], plan["K"])
+        b3 = b.permute([ib.index(c) for c in batch + con + bf]).reshape(plan["B"], plan["K"], plan["N"])
+        nat = batch + af + bf
+        got = torch.bmm(a3, b3).reshape([plan["size"][c] for c in nat]).permute([nat.index(c) for c in plan["out"]])
+        torch.testing.assert_close(got, torch.einsum(eq, a, b), rtol=1e-5, atol=1e-5)
+    for eq, sa, sb in [("ij,jk", (4, 8), (8, 8)), ("...ij,...jk->...ik", (2, 4, 8), (2, 8, 8)), ("ij,jk->k", (4, 8), (8, 8)),
+                       ("ii,ij->ij", (8, 8), (8, 8)), ("ij,ij->ij", (8, 8), (8, 8)), ("bij,cjk->bik", (1, 4, 8), (3, 8, 8))]:
+        assert fusion.einsum_plan(eq, sa, sb) is None, eq
+
+    class Mixer(torch.nn.Module):
+        def forward(self, x, w, y):
+            h = torch.einsum("bld,dn->bln", x, w)
+            return torch.einsum("bln,bmn->blm", h, y) + torch.einsum("bld,bld->bl", x, x).unsqueeze(-1)
+
+    x, w, y = (torch.randn(*s).to(torch.bfloat16) for s in ((2, 16, 32), (32, 40), (2, 24, 40)))
+    gm = capture(Mixer(), x, w, y)
+    leaves = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is fusion.hb_einsum]
+    assert len(leaves) == 2 and [n.args[0] for n in leaves] == ["bld,dn->bln", "bln,bmn->blm"]
+    assert sum(1 for t in targets(gm) if getattr(t, "__name__", "") == "einsum") == 1   # the row-wise dot stays
+    gm32 = capture(Mixer(), x.float(), w.float(), y.float())
+    assert not any(n.target is fusion.hb_einsum for n in gm32.graph.nodes)

@@ -247,3 +247,48 @@ def test_bmm_rejects_what_it_cannot_take(ops):
         ops.bmm(a, b)
     with pytest.raises(TypeError):
         ops.bmm(a.float(), b.float())
+
+
+@pytest.mark.parametrize("eq,sa,sb", [("bhid,bhjd->bhij", (2, 3, 80, 64), (2, 3, 72, 64)),
+                                      ("bhij,bhjd->bhid", (2, 3, 80, 72), (2, 3, 72, 64)),
+                                      ("bld,dn->bln", (3, 50, 128), (128, 200)),
+                                      ("ibk,kjb->bji", (40, 2, 64), (64, 24, 2))])
+def test_einsum_leaf_on_the_batched_gemm(ops, eq, sa, sb):
+    """hb_einsum (one launch of the batched GEMM) against fp32 einsum of the same 16-bit operands."""
+    from heddle_b200.frontend import fusion
+
+    g = torch.Generator().manual_seed(len(eq) + sum(sa))
+    a = torch.randn(*sa, generator=g).to(torch.bfloat16)
+    b = (torch.randn(*sb, generator=g) * 0.1).to(torch.bfloat16)
+    out = fusion.hb_einsum(eq, a.cuda(), b.cuda())
+    ref = torch.einsum(eq, a.float(), b.float())
+    assert tuple(out.shape) == tuple(ref.shape)
+    _close(out, ref, tol=1e-2)
+    assert ops.status_word() == 0
+
+
+def test_compiled_module_with_einsums(ops):
+    class Mixer(torch.nn.Module):
+        def forward(self, x, w, y):
+            h = torch.einsum("bld,dn->bln", x, w)
+            return torch.einsum("bln,bmn->blm", h, y)
+
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(2, 96, 128, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(128, 160, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    y = (torch.randn(2, 72, 160, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    m = Mixer()
+    ref = torch.einsum("bln,bmn->blm", torch.einsum("bld,dn->bln", x.float(), w.float()).to(torch.bfloat16).float(), y.float())
+    from heddle_b200.frontend import fusion, tilelang_backend
+    seen = []
+
+    def backend(gm, example_inputs):
+        out = tilelang_backend(gm, example_inputs)
+        seen.extend(n.target for n in out.graph.nodes if n.op == "call_function")
+        return out
+
+    torch._dynamo.reset()
+    with torch.no_grad():
+        out = torch.compile(m, backend=backend)(x, w, y)
+    assert seen.count(fusion.hb_einsum) == 2
+    _close(out, ref.cpu(), tol=1e-2)
