@@ -94,8 +94,11 @@ class GemmArgs(C.Structure):
         ("stream", C.c_void_p),
         ("batch", C.c_int32), ("w_layout", C.c_int32),
         ("a_batch_stride", C.c_int64), ("w_batch_stride", C.c_int64), ("o_batch_stride", C.c_int64),
-        ("r_batch_stride", C.c_int64),
+        ("r_batch_stride", C.c_int64), ("schedule", C.c_int32),
     ]
+
+
+GEMM_SCHEDULES = {"auto": 0, "single": 1, "pair": 2}
 
 
 class PrepareArgs(C.Structure):

@@ -22,8 +22,34 @@ static int launch_gemm(const GemmParams& p, int grid, const DeviceState* st, cud
   return HB_OK;
 }
 
+template <typename T, int EPI>
+static int launch_gemm_pair(const GemmParams& p, int grid, const DeviceState* st, cudaStream_t stream) {
+  if ((int)sizeof(GemmPairSmem) > st->smem_optin)
+    return set_error(HB_ERR_UNSUPPORTED, "hb_gemm_epilogue: kernel needs %d bytes of shared memory, device offers %d",
+                     (int)sizeof(GemmPairSmem), st->smem_optin);
+  auto kernel = gemm_pair_kernel<T, EPI>;
+  static bool configured[64] = {};
+  if (!configured[st->device & 63]) {
+    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GemmPairSmem)));
+    configured[st->device & 63] = true;
+  }
+  kernel<<<grid, kGemmThreads, sizeof(GemmPairSmem), stream>>>(p);  // clusters of two CTAs (compile-time attribute)
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB_OK;
+}
+
 template <typename T>
-static int dispatch_gemm(int epi_class, const GemmParams& p, int grid, const DeviceState* st, cudaStream_t stream) {
+static int dispatch_gemm(int epi_class, const GemmParams& p, int grid, bool pair, const DeviceState* st, cudaStream_t stream) {
+  if (pair) {
+    switch (epi_class) {
+      case kEpiPlain:
+        return launch_gemm_pair<T, kEpiPlain>(p, grid, st, stream);
+      case kEpiSwiglu:
+        return launch_gemm_pair<T, kEpiSwiglu>(p, grid, st, stream);
+      default:
+        return launch_gemm_pair<T, kEpiRope>(p, grid, st, stream);
+    }
+  }
   switch (epi_class) {
     case kEpiPlain:
       return launch_gemm<T, kEpiPlain>(p, grid, st, stream);
@@ -61,6 +87,8 @@ static int gemm_impl(const hb_gemm_args* a) {
     if ((reinterpret_cast<uintptr_t>(a->rope_cos) & 15) != 0 || (reinterpret_cast<uintptr_t>(a->rope_sin) & 15) != 0)
       return set_error(HB_ERR_ALIGN, "hb_gemm_epilogue: ROPE tables need 16-byte alignment");
   }
+  if (a->schedule < HB_GEMM_AUTO || a->schedule > HB_GEMM_PAIR)
+    return set_error(HB_ERR_BAD_ARG, "hb_gemm_epilogue: unknown schedule %d", a->schedule);
   const int batch = a->batch > 0 ? a->batch : 1;
   const bool w_kn = a->w_layout == HB_W_KN;
   if (a->w_layout != HB_W_NK && a->w_layout != HB_W_KN)
@@ -136,7 +164,10 @@ static int gemm_impl(const hb_gemm_args* a) {
   p.N_out = n_out;
   p.K = a->K;
   p.tile_cols = epi_class == kEpiSwiglu ? 128 : kGemmBN;
-  p.tiles_m = (a->M + kGemmBM - 1) / kGemmBM;
+  // CTA pairs (256-row tiles) whenever a problem has more than one 128-row tile of rows
+  const bool pair = a->schedule == HB_GEMM_PAIR || (a->schedule == HB_GEMM_AUTO && a->M > kGemmBM && st->sm_count >= 2);
+  const int tile_rows = pair ? kPairBM : kGemmBM;
+  p.tiles_m = (a->M + tile_rows - 1) / tile_rows;
   p.tiles_n = (n_out + p.tile_cols - 1) / p.tile_cols;
   p.tiles_per_batch = p.tiles_m * p.tiles_n;
   const long long tiles = (long long)p.tiles_m * p.tiles_n * batch;
@@ -154,10 +185,10 @@ static int gemm_impl(const hb_gemm_args* a) {
   p.rope_cols = a->rope_cols;
   p.w_row2_offset = n_out;
 
-  const int grid = (int)std::min<long long>(tiles, st->sm_count);
+  const int grid = pair ? 2 * (int)std::min<long long>(tiles, st->sm_count / 2) : (int)std::min<long long>(tiles, st->sm_count);
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  return a->dtype == HB_BF16 ? dispatch_gemm<__nv_bfloat16>(epi_class, p, grid, st, stream)
-                             : dispatch_gemm<__half>(epi_class, p, grid, st, stream);
+  return a->dtype == HB_BF16 ? dispatch_gemm<__nv_bfloat16>(epi_class, p, grid, pair, st, stream)
+                             : dispatch_gemm<__half>(epi_class, p, grid, pair, st, stream);
 }
 
 static int rowstat_impl(const void* x, const void* residual, void* y_out, float* rstd, int M, int N, long long ldx,

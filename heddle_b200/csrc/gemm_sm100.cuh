@@ -177,10 +177,12 @@ __device__ __forceinline__ void load_bias8(const GemmParams& p, int col, float (
 
 // Epilogue of one accumulator tile for the row owned by this thread.  `tacc` carries the
 // warp's TMEM lane offset and the accumulator buffer's first column.  Two warpgroups share a
-// tile: `part` (0 or 1) selects this thread's half of the output columns.
+// tile: `part` (0 or 1) selects this thread's half of the output columns.  `release` is the
+// shared::cluster address of the barrier that hands the accumulator buffer back to the MMA warp
+// (this CTA's own, or the leader's when a CTA pair shares the MMA).
 template <typename T, int EPI>
 __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t tacc, int b, int m0, int n0,
-                                                  int row_in_tile, int part, uint8_t* stage_base, uint64_t* release) {
+                                                  int row_in_tile, int part, uint8_t* stage_base, uint32_t release) {
   const int row = m0 + row_in_tile;
   const bool row_ok = row < p.M;
   const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[(long long)b * p.M + row] : 1.0f;
@@ -196,7 +198,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
     tmem_wait_ld();
     tc_fence_before();
     __syncwarp();
-    if ((threadIdx.x & 31) == 0) mbar_arrive(release);
+    if ((threadIdx.x & 31) == 0) mbar_arrive_cluster(release);
     // Coalesced stores: the warpgroup's 128 rows x 64 columns go to shared memory in the 128-byte
     // swizzled layout (a thread writes its own row: conflict-free), one thread hands the slab to the
     // TMA, which clips rows past M and columns past N_out.  Two slabs per tile and warpgroup.
@@ -233,7 +235,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
       }
       fence_proxy_async();
       named_bar_sync(1 + part, 128);
-      if (issuer && col0 < p.N_out) {
+      if (issuer && col0 < p.N_out && m0 < p.M) {
         tma_store_3d(&p.tm_out, stage, col0, m0, b);
         tma_store_commit();
       }
@@ -250,7 +252,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
     tmem_wait_ld();
     tc_fence_before();
     __syncwarp();
-    if ((threadIdx.x & 31) == 0) mbar_arrive(release);
+    if ((threadIdx.x & 31) == 0) mbar_arrive_cluster(release);
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
       const int col = n0 + (part * 2 + cc) * 32;
@@ -333,7 +335,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
     auto release_acc = [&]() {
       tc_fence_before();
       __syncwarp();
-      if ((threadIdx.x & 31) == 0) mbar_arrive(release);
+      if ((threadIdx.x & 31) == 0) mbar_arrive_cluster(release);
     };
     if (split_heads) {
       // head_dim 64 or 128: the warpgroup's 128 columns are read with one wait and the accumulator is
@@ -505,7 +507,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       if (!mbar_wait_warp(&s.acc_full[acc], (tile_i >> 1) & 1, ctx, kGemmRoleEpi)) break;
       tc_fence_after();
       gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, b, m_t * kGemmBM, n_t * p.tile_cols,
-                                quarter * 32 + lane, (warp - 2) >> 2, s.stage_out[(warp - 2) >> 2], &s.acc_empty[acc]);
+                                quarter * 32 + lane, (warp - 2) >> 2, s.stage_out[(warp - 2) >> 2], smem_u32(&s.acc_empty[acc]));
       // the epilogue hands the accumulator buffer back itself (acc_empty), as soon as it has read it
     }
     // the slabs handed to the TMA must have been written out before shared memory goes away
@@ -517,6 +519,233 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// The same GEMM on CTA pairs: a cluster of two CTAs owns a 256 x 256 accumulator tile and the
+// leader's MMA warp issues tcgen05.mma.cta_group::2 (M = 256).  Each CTA loads only its own 128 rows
+// of A and its own 128 of the tile's 256 B rows (plain tiled TMA loads, no multicast) and holds its
+// 128 x 256 half of the accumulator in its own TMEM, so a CTA moves 32 KB per K step of 64 through
+// shared memory instead of 48 KB and the ring is 6 stages deep.  Epilogues are the single-CTA ones.
+//
+// Barriers: the leader's full[s] counts the bytes of both CTAs' loads; empty[s] and acc_full[a] exist in
+// both CTAs and the leader's MMA warp commits to each (two commits, no multicast); the leader's
+// acc_empty[a] collects the 8 epilogue warps of both CTAs.  Every wait is on a barrier of the waiting
+// CTA and is bounded like the single-CTA kernel's.  Before a CTA leaves, its producer has seen every
+// commit aimed at its ring, the leader has seen every release aimed at it, and the pair meets at a
+// cluster barrier, so nothing can arrive at shared memory that is gone.
+// ------------------------------------------------------------------------------------------
+constexpr int kPairStages = 6;
+constexpr int kPairBM = 256;  // rows of a pair's tile (128 per CTA)
+
+struct GemmPairSmem {
+  alignas(1024) uint8_t a[kPairStages][kGemmBM * kGemmBK * 2];
+  alignas(1024) uint8_t b[kPairStages][(kGemmBN / 2) * kGemmBK * 2];
+  alignas(1024) uint8_t stage_out[2][kGemmBM * 128];
+  uint64_t full[kPairStages], empty[kPairStages];
+  uint64_t acc_full[2], acc_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+// bounded wait that also orders against the peer CTA's arrivals
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, uint32_t role) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++spins & 0xFFu) == 0u) {
+      if (*ctx.cta_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > ctx.limit_ns) {
+        raise_abort(ctx, kStatusWaitTimeout | role);
+        return false;
+      }
+    }
+  }
+}
+
+// tile t of the pair grid: tiles_m counts 256-row tiles
+__device__ __forceinline__ void gemm_pair_tile_coords(const GemmParams& p, int t, int& m_t, int& n_t, int& b) {
+  gemm_tile_coords(p, t, m_t, n_t, b);
+}
+
+template <typename T, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gemm_pair_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  GemmPairSmem& s = *reinterpret_cast<GemmPairSmem*>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  AbortCtx ctx{&s.abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    for (int i = 0; i < kPairStages; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.acc_full[i], 1);
+      mbar_init(&s.acc_empty[i], 16);  // 8 epilogue warps of each CTA (used in the leader only)
+    }
+    mbar_init(&s.drain, 1);
+    fence_mbar_init();
+    if ((smem_u32(smem_raw) & 1023u) != 0u) raise_abort(ctx, kStatusSmemMisaligned);
+    prefetch_tensormap(&p.tm_a);
+    prefetch_tensormap(&p.tm_w);
+    if (p.tma_store) prefetch_tensormap(&p.tm_out);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&s.tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anything arrives at them
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  const bool run = (s.abort_flag == 0);
+
+  if (warp == 0) {
+    if (run && lane == 0) {
+      // ---------------- TMA producer (both CTAs) ----------------
+      constexpr uint32_t kPairStageBytes = 2u * (kGemmBM + kGemmBN / 2) * kGemmBK * 2;  // both CTAs' loads
+      uint32_t st = 0, phase = 1;
+      bool ok = true;
+      for (int t = pair; ok && t < p.num_tiles; t += n_pairs) {
+        int m_t, n_t, b;
+        gemm_pair_tile_coords(p, t, m_t, n_t, b);
+        const int m0 = m_t * kPairBM + static_cast<int>(rank) * kGemmBM;
+        const int n0 = n_t * p.tile_cols;
+        // this CTA's 128 B rows: the first or the second half of a plain tile; the gate (leader) or the up
+        // (peer) rows of a SwiGLU tile
+        const int row_b = (EPI == kEpiSwiglu) ? (rank == 0 ? n0 : p.w_row2_offset + n0) : n0 + static_cast<int>(rank) * 128;
+        for (int ks = 0; ks < p.k_steps; ++ks) {
+          if (!mbar_wait(&s.empty[st], phase, ctx, kGemmRoleTma)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = mapa_u32(smem_u32(&s.full[st]), 0);
+          if (rank == 0) mbar_arrive_expect_tx(&s.full[st], kPairStageBytes);
+          tma_load_3d_pair(s.a[st], &p.tm_a, full_leader, ks * kGemmBK, m0, b);
+          if (p.w_kn) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              tma_load_3d_pair(s.b[st] + i * (kGemmBK * 128), &p.tm_w, full_leader, row_b + i * 64, ks * kGemmBK, b);
+          } else {
+            tma_load_3d_pair(s.b[st], &p.tm_w, full_leader, ks * kGemmBK, row_b, b);
+          }
+          if (++st == kPairStages) {
+            st = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      // tail: every commit aimed at this CTA's ring has arrived before the CTA may leave (a slot that
+      // was never filled passes at once)
+      for (int i = 0; ok && i < kPairStages; ++i) {
+        if (!mbar_wait(&s.empty[st], phase, ctx, kGemmRoleTma)) break;
+        if (++st == kPairStages) {
+          st = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (run && rank == 0) {
+      // ---------------- MMA issuer (leader CTA only) ----------------
+      constexpr uint32_t idesc_nk = make_idesc(Pack2<T>::kFormat, kPairBM, kGemmBN, 0, 0);
+      constexpr uint32_t idesc_kn = make_idesc(Pack2<T>::kFormat, kPairBM, kGemmBN, 0, 1);
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kLbo = (16u >> 4) << 16;
+      constexpr uint32_t kLboKn = ((kGemmBK * 128u) >> 4) << 16;
+      const uint32_t idesc = p.w_kn ? idesc_kn : idesc_nk;
+      const uint32_t b_lbo = p.w_kn ? kLboKn : kLbo;
+      const uint32_t b_step = p.w_kn ? (16u * 128u >> 4) : 2u;
+      const bool leader = elect_one();
+      uint32_t stage = 0, phase = 0, tile_i = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < p.num_tiles; t += n_pairs, ++tile_i) {
+        const uint32_t acc = tile_i & 1;
+        bool got = mbar_wait_cluster(&s.acc_empty[acc], ((tile_i >> 1) & 1) ^ 1, ctx, kGemmRoleMma);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + acc * kGemmBN;
+        for (int ks = 0; ks < p.k_steps; ++ks) {
+          if (!mbar_wait_warp(&s.full[stage], phase, ctx, kGemmRoleMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_lo = (smem_u32(s.a[stage]) >> 4) | kLbo, b_lo = (smem_u32(s.b[stage]) >> 4) | b_lbo;
+          if (leader) {
+#pragma unroll
+            for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+              umma_ss_f16_pair(d_tmem, (static_cast<uint64_t>(kDescHi) << 32) | (a_lo + kk * 2),
+                               (static_cast<uint64_t>(kDescHi) << 32) | (b_lo + kk * b_step), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            }
+            const uint32_t e = smem_u32(&s.empty[stage]);
+            umma_commit_pair(mapa_u32(e, 0));
+            umma_commit_pair(mapa_u32(e, 1));
+          }
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok && leader) {
+          const uint32_t f = smem_u32(&s.acc_full[acc]);
+          umma_commit_pair(mapa_u32(f, 0));
+          umma_commit_pair(mapa_u32(f, 1));
+        }
+      }
+      // tail: the peer's last releases have arrived here before the leader may leave
+      for (uint32_t a = 0; ok && a < 2 && a < tile_i; ++a) {
+        const uint32_t uses = (tile_i + 1 - a) >> 1;  // tiles that used buffer a
+        bool got = mbar_wait_cluster(&s.acc_empty[a], (uses - 1) & 1, ctx, kGemmRoleMma);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) break;
+      }
+      __syncwarp();
+      if (s.abort_flag && lane == 0) {
+        umma_commit_pair(mapa_u32(smem_u32(&s.drain), 0));
+        mbar_wait(&s.drain, 0, ctx, kGemmRoleDrain);
+      }
+    }
+    __syncwarp();
+  } else if (run) {
+    // ---------------- epilogue warps (both CTAs, each on its own 128 rows) ----------------
+    const int quarter = warp & 3;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    uint32_t tile_i = 0;
+    for (int t = pair; t < p.num_tiles; t += n_pairs, ++tile_i) {
+      int m_t, n_t, b;
+      gemm_pair_tile_coords(p, t, m_t, n_t, b);
+      const uint32_t acc = tile_i & 1;
+      if (!mbar_wait_warp(&s.acc_full[acc], (tile_i >> 1) & 1, ctx, kGemmRoleEpi)) break;
+      tc_fence_after();
+      gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, b, m_t * kPairBM + static_cast<int>(rank) * kGemmBM,
+                                n_t * p.tile_cols, quarter * 32 + lane, (warp - 2) >> 2, s.stage_out[(warp - 2) >> 2],
+                                mapa_u32(smem_u32(&s.acc_empty[acc]), 0));
+    }
+    if (p.tma_store && quarter == 0 && lane == 0) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before();
+  cluster_sync_all();  // the leader's MMAs read the peer's shared memory: nobody leaves before all are done
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem, 512);
   }
 }
 

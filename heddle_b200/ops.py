@@ -6,6 +6,7 @@ There is no CPU or eager fallback here: CPU tensors are rejected.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import math
 from typing import Optional, Sequence, Tuple
 
@@ -217,6 +218,19 @@ def debug_umma(mode: int, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return out
 
 
+# Which GEMM kernel hb_gemm_epilogue runs: "auto" (CTA pairs when M > 128), "single" or "pair".
+_gemm_schedule = os.environ.get("HEDDLE_B200_GEMM_SCHEDULE", "auto")
+
+
+def set_gemm_schedule(name: str) -> str:
+    """Select the GEMM kernel for later calls ("auto", "single", "pair"); returns the previous choice."""
+    global _gemm_schedule
+    if name not in _lib.GEMM_SCHEDULES:
+        raise ValueError(f"unknown GEMM schedule {name!r}")
+    prev, _gemm_schedule = _gemm_schedule, name
+    return prev
+
+
 def gemm_epilogue(a: torch.Tensor, w: torch.Tensor, epilogue: str = "none", *,
                   bias: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
                   residual: Optional[torch.Tensor] = None,
@@ -288,6 +302,7 @@ def gemm_epilogue(a: torch.Tensor, w: torch.Tensor, epilogue: str = "none", *,
         g.rope_seq, g.head_dim, g.rope_cols = cos.shape[0], int(hd), int(rope_cols)
     g.stream = _stream_ptr(a.device)
     with torch.cuda.device(a.device):
+        g.schedule = _lib.GEMM_SCHEDULES[_gemm_schedule]
         _lib.check(_lib.load().hb_gemm_epilogue(C.byref(g)))
     return out2.reshape(*lead, n_out) if out is None else out
 
@@ -346,6 +361,7 @@ def bmm(a: torch.Tensor, b: torch.Tensor, epilogue: str = "none", *, bias: Optio
         g.residual, g.ldr, g.r_batch_stride = r.data_ptr(), N, M * N
     g.stream = _stream_ptr(a.device)
     with torch.cuda.device(a.device):
+        g.schedule = _lib.GEMM_SCHEDULES[_gemm_schedule]
         _lib.check(_lib.load().hb_gemm_epilogue(C.byref(g)))
     return out
 

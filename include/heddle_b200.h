@@ -185,6 +185,10 @@ typedef enum hb_epilogue {
 } hb_epilogue;
 
 typedef enum hb_w_layout { HB_W_NK = 0, HB_W_KN = 1 } hb_w_layout;
+/* Which kernel runs the product.  AUTO: CTA pairs (two CTAs share a 256 x 256 tile through
+ * tcgen05.mma.cta_group::2) when M > 128, else the single-CTA kernel (128 x 256 tiles).  SINGLE and
+ * PAIR force one of them; the results are identical (same accumulation order per element). */
+typedef enum hb_gemm_schedule { HB_GEMM_AUTO = 0, HB_GEMM_SINGLE = 1, HB_GEMM_PAIR = 2 } hb_gemm_schedule;
 
 typedef struct hb_gemm_args {
   const void* a; /* [M, K], row stride lda */
@@ -213,6 +217,7 @@ typedef struct hb_gemm_args {
   int32_t batch;
   int32_t w_layout;
   int64_t a_batch_stride, w_batch_stride, o_batch_stride, r_batch_stride;
+  int32_t schedule; /* hb_gemm_schedule */
 } hb_gemm_args;
 
 int hb_gemm_epilogue(const hb_gemm_args* args);
