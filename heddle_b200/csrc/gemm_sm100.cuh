@@ -38,7 +38,10 @@ constexpr int kGemmBM = 128;
 constexpr int kGemmBN = 256;
 constexpr int kGemmBK = 64;
 constexpr int kGemmStages = 4;
-constexpr int kGemmGroupM = 16;  // M-tiles per rasterisation group (L2 reuse of the weight slabs)
+#ifndef HB_GEMM_GROUP_M
+#define HB_GEMM_GROUP_M 16
+#endif
+constexpr int kGemmGroupM = HB_GEMM_GROUP_M;  // M-tiles per rasterisation group (L2 reuse of the weight slabs)
 
 enum GemmEpiClass : int { kEpiPlain = 0, kEpiSwiglu = 1, kEpiRope = 2 };
 enum GemmAct : int { kActNone = 0, kActSilu = 1, kActRelu = 2, kActGeluTanh = 3, kActSigmoid = 4, kActTanh = 5 };
@@ -536,7 +539,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
 // commit aimed at its ring, the leader has seen every release aimed at it, and the pair meets at a
 // cluster barrier, so nothing can arrive at shared memory that is gone.
 // ------------------------------------------------------------------------------------------
-constexpr int kPairStages = 6;
+#ifndef HB_PAIR_STAGES
+#define HB_PAIR_STAGES 6
+#endif
+constexpr int kPairStages = HB_PAIR_STAGES;
 constexpr int kPairBM = 256;  // rows of a pair's tile (128 per CTA)
 
 struct GemmPairSmem {

@@ -49,7 +49,8 @@ int main(void) {
          offsetof(hb_prepare_args, stream));
   printf("%zu %zu %zu %zu %zu\n", sizeof(hb_fa_bwd_args), offsetof(hb_fa_bwd_args, B), offsetof(hb_fa_bwd_args, q_stride_b),
          offsetof(hb_fa_bwd_args, causal), offsetof(hb_fa_bwd_args, stream));
-  printf("%zu %zu %zu\n", offsetof(hb_gemm_args, batch), offsetof(hb_gemm_args, w_layout), offsetof(hb_gemm_args, r_batch_stride));
+  printf("%zu %zu %zu %zu\n", offsetof(hb_gemm_args, batch), offsetof(hb_gemm_args, w_layout), offsetof(hb_gemm_args, r_batch_stride),
+         offsetof(hb_gemm_args, schedule));
   printf("%zu %zu %zu %zu %zu %zu %zu\n", sizeof(hb_rowwise_args), offsetof(hb_rowwise_args, rowscalar), offsetof(hb_rowwise_args, n_inputs),
          offsetof(hb_rowwise_args, rows), offsetof(hb_rowwise_args, program), offsetof(hb_rowwise_args, stream),
          offsetof(hb_rowwise_args, mode));
@@ -75,7 +76,8 @@ int main(void) {
     assert bw == [ctypes.sizeof(_lib.FaBwdArgs), _lib.FaBwdArgs.B.offset, _lib.FaBwdArgs.q_stride_b.offset,
                   _lib.FaBwdArgs.causal.offset, _lib.FaBwdArgs.stream.offset]
     gb = [int(x) for x in lines[5].split()]
-    assert gb == [_lib.GemmArgs.batch.offset, _lib.GemmArgs.w_layout.offset, _lib.GemmArgs.r_batch_stride.offset]
+    assert gb == [_lib.GemmArgs.batch.offset, _lib.GemmArgs.w_layout.offset, _lib.GemmArgs.r_batch_stride.offset,
+                  _lib.GemmArgs.schedule.offset]
     rw = [int(x) for x in lines[6].split()]
     assert rw == [ctypes.sizeof(_lib.RowwiseArgs), _lib.RowwiseArgs.rowscalar.offset, _lib.RowwiseArgs.n_inputs.offset,
                   _lib.RowwiseArgs.rows.offset, _lib.RowwiseArgs.program.offset, _lib.RowwiseArgs.stream.offset,

@@ -9,10 +9,15 @@ from oracle import attention_oracle as O
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def ops(built_lib):
+@pytest.fixture(scope="module", params=["single", "pair"])
+def ops(built_lib, request):
+    """Every test of this module runs on the single-CTA kernel (128 x 256 tiles) and on CTA pairs
+    (tcgen05.mma.cta_group::2, 256 x 256 tiles; forced also where M <= 128 leaves the peer CTA only
+    out-of-range rows)."""
     from heddle_b200 import ops as _ops
-    return _ops
+    prev = _ops.set_gemm_schedule(request.param)
+    yield _ops
+    _ops.set_gemm_schedule(prev)
 
 
 def _close(out, ref, tol=2e-2):
@@ -292,3 +297,29 @@ def test_compiled_module_with_einsums(ops):
         out = torch.compile(m, backend=backend)(x, w, y)
     assert seen.count(fusion.hb_einsum) == 2
     _close(out, ref.cpu(), tol=1e-2)
+
+
+def test_cta_pairs_and_single_cta_kernels_agree_bitwise(ops):
+    """Both kernels accumulate every output element over K in the same order: equal bits."""
+    g = torch.Generator().manual_seed(31)
+    cases = [(300, 264, 200, "none"), (2048, 1024, 1024, "gelu_tanh"), (640, 512, 320, "swiglu"), (100, 512, 72, "none")]
+    prev = ops.set_gemm_schedule("single")
+    try:
+        for M, N, K, epi in cases:
+            a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+            w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+            ops.set_gemm_schedule("single")
+            one = ops.gemm_epilogue(a, w, epi)
+            ops.set_gemm_schedule("pair")
+            two = ops.gemm_epilogue(a, w, epi)
+            assert torch.equal(one, two), (M, N, K, epi)
+        b3 = (torch.randn(3, 136, 200, generator=g) * 0.05).to(torch.bfloat16).cuda()   # [B, K, N] row-major
+        a3 = torch.randn(3, 260, 136, generator=g).to(torch.bfloat16).cuda()
+        ops.set_gemm_schedule("single")
+        one = ops.bmm(a3, b3)
+        ops.set_gemm_schedule("pair")
+        two = ops.bmm(a3, b3)
+        assert torch.equal(one, two)
+        assert ops.status_word() == 0
+    finally:
+        ops.set_gemm_schedule(prev)
