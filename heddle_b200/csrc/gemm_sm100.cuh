@@ -70,6 +70,8 @@ struct alignas(64) GemmParams {
   int w_kn;           // 1: the second operand is [K, N] row-major
   long long o_batch_stride, r_batch_stride;  // elements between consecutive batches of out / residual
   int tma_store;      // PLAIN epilogue: results leave through shared memory and a TMA store
+  int pair_stages;    // CTA-pair kernel: depth of the operand ring (3..6) ...
+  int out_slabs;      // ... and staging slabs per epilogue warpgroup (1, 2 or 4); stages + slabs = 7
 };
 
 struct GemmSmem {
@@ -185,7 +187,8 @@ __device__ __forceinline__ void load_bias8(const GemmParams& p, int col, float (
 // (this CTA's own, or the leader's when a CTA pair shares the MMA).
 template <typename T, int EPI>
 __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t tacc, int b, int m0, int n0,
-                                                  int row_in_tile, int part, uint8_t* stage_base, uint32_t release) {
+                                                  int row_in_tile, int part, uint8_t* stage_base, int n_slabs, uint32_t& slab_cursor,
+                                                  uint32_t release) {
   const int row = m0 + row_in_tile;
   const bool row_ok = row < p.M;
   const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[(long long)b * p.M + row] : 1.0f;
@@ -205,13 +208,41 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
     // Coalesced stores: the warpgroup's 128 rows x 64 columns go to shared memory in the 128-byte
     // swizzled layout (a thread writes its own row: conflict-free), one thread hands the slab to the
     // TMA, which clips rows past M and columns past N_out.  Two slabs per tile and warpgroup.
-    uint8_t* stage = stage_base;
+    // The warpgroup owns a ring of `n_slabs` staging slabs; a slab is rewritten once the TMA store that
+    // last used it has read it (`wait_group.read` with n_slabs - 1 younger groups allowed in flight), so
+    // with several slabs the stores of consecutive slabs and tiles overlap (products with a short K loop
+    // are bound by this path).  Every slab commits a group, stored or not, to keep that count exact.
     const bool issuer = row_in_tile == 0;
+    const bool raw = p.row_scale == nullptr && p.bias == nullptr && p.residual == nullptr && p.act == kActNone;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
       const int col0 = n0 + part * (kGemmBN / 2) + cc * 64;
-      if (issuer) tma_store_wait_read<0>();  // the previous slab has left shared memory
+      uint8_t* stage = stage_base + (slab_cursor % static_cast<uint32_t>(n_slabs)) * (kGemmBM * 128);
+      ++slab_cursor;
+      if (issuer) {
+        if (n_slabs == 1) tma_store_wait_read<0>();
+        else if (n_slabs == 2) tma_store_wait_read<1>();
+        else tma_store_wait_read<3>();
+      }
       named_bar_sync(1 + part, 128);
+      if (raw) {
+        // nothing to apply: round and store (products with a short K loop are bound by this path's
+        // instruction count, so it carries no scale, bias, activation or residual tests)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t* x = &r[cc * 2 + h][g * 8];
+            uint4 w;
+            w.x = Pack2<T>::pack(__uint_as_float(x[0]), __uint_as_float(x[1]));
+            w.y = Pack2<T>::pack(__uint_as_float(x[2]), __uint_as_float(x[3]));
+            w.z = Pack2<T>::pack(__uint_as_float(x[4]), __uint_as_float(x[5]));
+            w.w = Pack2<T>::pack(__uint_as_float(x[6]), __uint_as_float(x[7]));
+            const int chunk = (h * 4 + g) ^ (row_in_tile & 7);
+            *reinterpret_cast<uint4*>(stage + row_in_tile * 128 + chunk * 16) = w;
+          }
+        }
+      } else {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int col = col0 + h * 32;
@@ -236,10 +267,11 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmParams& p, uint32_t 
           *reinterpret_cast<uint4*>(stage + row_in_tile * 128 + chunk * 16) = pack8<T>(v);
         }
       }
+      }
       fence_proxy_async();
       named_bar_sync(1 + part, 128);
-      if (issuer && col0 < p.N_out && m0 < p.M) {
-        tma_store_3d(&p.tm_out, stage, col0, m0, b);
+      if (issuer) {
+        if (col0 < p.N_out && m0 < p.M) tma_store_3d(&p.tm_out, stage, col0, m0, b);
         tma_store_commit();
       }
     }
@@ -502,7 +534,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     // ---------------- epilogue warps ----------------
     const int quarter = warp & 3;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    uint32_t tile_i = 0;
+    uint32_t tile_i = 0, slab_cursor = 0;
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++tile_i) {
       int m_t, n_t, b;
       gemm_tile_coords(p, t, m_t, n_t, b);
@@ -510,7 +542,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
       if (!mbar_wait_warp(&s.acc_full[acc], (tile_i >> 1) & 1, ctx, kGemmRoleEpi)) break;
       tc_fence_after();
       gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, b, m_t * kGemmBM, n_t * p.tile_cols,
-                                quarter * 32 + lane, (warp - 2) >> 2, s.stage_out[(warp - 2) >> 2], smem_u32(&s.acc_empty[acc]));
+                                quarter * 32 + lane, (warp - 2) >> 2, s.stage_out[(warp - 2) >> 2], 1, slab_cursor,
+                                smem_u32(&s.acc_empty[acc]));
       // the epilogue hands the accumulator buffer back itself (acc_empty), as soon as it has read it
     }
     // the slabs handed to the TMA must have been written out before shared memory goes away
@@ -539,22 +572,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
 // commit aimed at its ring, the leader has seen every release aimed at it, and the pair meets at a
 // cluster barrier, so nothing can arrive at shared memory that is gone.
 // ------------------------------------------------------------------------------------------
-#ifndef HB_PAIR_STAGES
-#define HB_PAIR_STAGES 6
-#endif
-constexpr int kPairStages = HB_PAIR_STAGES;
 constexpr int kPairBM = 256;  // rows of a pair's tile (128 per CTA)
+constexpr int kPairMaxStages = 6;
+constexpr int kPairSlots = 7;              // 32 KB slots of shared memory: ring stages + staging slabs per warpgroup
+constexpr int kPairStageA = kGemmBM * kGemmBK * 2;        // 16 KB
+constexpr int kPairStageB = (kGemmBN / 2) * kGemmBK * 2;  // 16 KB
+constexpr int kPairSlab = kGemmBM * 128;                  // 16 KB: 128 rows x 64 columns
 
-struct GemmPairSmem {
-  alignas(1024) uint8_t a[kPairStages][kGemmBM * kGemmBK * 2];
-  alignas(1024) uint8_t b[kPairStages][(kGemmBN / 2) * kGemmBK * 2];
-  alignas(1024) uint8_t stage_out[2][kGemmBM * 128];
-  uint64_t full[kPairStages], empty[kPairStages];
+// Shared memory of the pair kernel, carved at run time: [A ring][B ring][staging slabs: warpgroup 0, 1][control].
+// Long K loops get the deepest ring and one slab per warpgroup; short ones, which are bound by the stores,
+// trade ring stages for slabs (GemmParams::pair_stages / out_slabs).
+struct GemmPairCtrl {
+  uint64_t full[kPairMaxStages], empty[kPairMaxStages];
   uint64_t acc_full[2], acc_empty[2];
   uint64_t drain;
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
+constexpr int kPairSmemBytes = kPairSlots * 32768 + static_cast<int>(sizeof(GemmPairCtrl));
 
 // bounded wait that also orders against the peer CTA's arrivals
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, uint32_t role) {
@@ -584,7 +619,11 @@ __device__ __forceinline__ void gemm_pair_tile_coords(const GemmParams& p, int t
 template <typename T, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gemm_pair_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  GemmPairSmem& s = *reinterpret_cast<GemmPairSmem*>(smem_raw);
+  const int kStages = p.pair_stages;
+  uint8_t* const ring_a = smem_raw;
+  uint8_t* const ring_b = ring_a + kStages * kPairStageA;
+  uint8_t* const slabs = ring_b + kStages * kPairStageB;
+  GemmPairCtrl& s = *reinterpret_cast<GemmPairCtrl*>(smem_raw + kPairSlots * 32768);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
@@ -592,7 +631,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
 
   if (threadIdx.x == 0) {
     s.abort_flag = 0;
-    for (int i = 0; i < kPairStages; ++i) {
+    for (int i = 0; i < kPairMaxStages; ++i) {
       mbar_init(&s.full[i], 1);
       mbar_init(&s.empty[i], 1);
     }
@@ -638,15 +677,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
           }
           const uint32_t full_leader = mapa_u32(smem_u32(&s.full[st]), 0);
           if (rank == 0) mbar_arrive_expect_tx(&s.full[st], kPairStageBytes);
-          tma_load_3d_pair(s.a[st], &p.tm_a, full_leader, ks * kGemmBK, m0, b);
+          tma_load_3d_pair(ring_a + st * kPairStageA, &p.tm_a, full_leader, ks * kGemmBK, m0, b);
           if (p.w_kn) {
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-              tma_load_3d_pair(s.b[st] + i * (kGemmBK * 128), &p.tm_w, full_leader, row_b + i * 64, ks * kGemmBK, b);
+              tma_load_3d_pair(ring_b + st * kPairStageB + i * (kGemmBK * 128), &p.tm_w, full_leader, row_b + i * 64, ks * kGemmBK, b);
           } else {
-            tma_load_3d_pair(s.b[st], &p.tm_w, full_leader, ks * kGemmBK, row_b, b);
+            tma_load_3d_pair(ring_b + st * kPairStageB, &p.tm_w, full_leader, ks * kGemmBK, row_b, b);
           }
-          if (++st == kPairStages) {
+          if (++st == static_cast<uint32_t>(kStages)) {
             st = 0;
             phase ^= 1;
           }
@@ -654,9 +693,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
       }
       // tail: every commit aimed at this CTA's ring has arrived before the CTA may leave (a slot that
       // was never filled passes at once)
-      for (int i = 0; ok && i < kPairStages; ++i) {
+      for (int i = 0; ok && i < kStages; ++i) {
         if (!mbar_wait(&s.empty[st], phase, ctx, kGemmRoleTma)) break;
-        if (++st == kPairStages) {
+        if (++st == static_cast<uint32_t>(kStages)) {
           st = 0;
           phase ^= 1;
         }
@@ -693,7 +732,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
             break;
           }
           tc_fence_after();
-          const uint32_t a_lo = (smem_u32(s.a[stage]) >> 4) | kLbo, b_lo = (smem_u32(s.b[stage]) >> 4) | b_lbo;
+          const uint32_t a_lo = (smem_u32(ring_a + stage * kPairStageA) >> 4) | kLbo;
+          const uint32_t b_lo = (smem_u32(ring_b + stage * kPairStageB) >> 4) | b_lbo;
           if (leader) {
 #pragma unroll
             for (int kk = 0; kk < kGemmBK / 16; ++kk) {
@@ -704,7 +744,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
             umma_commit_pair(mapa_u32(e, 0));
             umma_commit_pair(mapa_u32(e, 1));
           }
-          if (++stage == kPairStages) {
+          if (++stage == static_cast<uint32_t>(kStages)) {
             stage = 0;
             phase ^= 1;
           }
@@ -733,7 +773,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
     // ---------------- epilogue warps (both CTAs, each on its own 128 rows) ----------------
     const int quarter = warp & 3;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    uint32_t tile_i = 0;
+    uint32_t tile_i = 0, slab_cursor = 0;
+    uint8_t* const my_slabs = slabs + ((warp - 2) >> 2) * p.out_slabs * kPairSlab;
     for (int t = pair; t < p.num_tiles; t += n_pairs, ++tile_i) {
       int m_t, n_t, b;
       gemm_pair_tile_coords(p, t, m_t, n_t, b);
@@ -741,7 +782,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
       if (!mbar_wait_warp(&s.acc_full[acc], (tile_i >> 1) & 1, ctx, kGemmRoleEpi)) break;
       tc_fence_after();
       gemm_epilogue_row<T, EPI>(p, tmem + lane_off + acc * kGemmBN, b, m_t * kPairBM + static_cast<int>(rank) * kGemmBM,
-                                n_t * p.tile_cols, quarter * 32 + lane, (warp - 2) >> 2, s.stage_out[(warp - 2) >> 2],
+                                n_t * p.tile_cols, quarter * 32 + lane, (warp - 2) >> 2, my_slabs, p.out_slabs, slab_cursor,
                                 mapa_u32(smem_u32(&s.acc_empty[acc]), 0));
     }
     if (p.tma_store && quarter == 0 && lane == 0) tma_store_wait_all<0>();
