@@ -334,7 +334,14 @@ def run_secondary(peaks) -> dict:
             ("h2o", False), ("rowprog", False)]
     for name, check in plan:
         try:
-            r = bench_configs.run_config(name, steps=10 if name in ("c3", "c5", "gemm_plain") else 20, warmup=3, check=check)
+            # every configuration is a burst measurement like the headline: a short pause lets the part
+            # leave the power-capped state the previous configuration left it in (without it the runs at the
+            # end of the list read 30-45 % low), and the clocks seen during the run are reported with it
+            torch.cuda.synchronize()
+            time.sleep(0.5)
+            with ClockSampler(torch.cuda.current_device()) as cs:
+                r = bench_configs.run_config(name, steps=10 if name in ("c3", "c5", "gemm_plain") else 20, warmup=3, check=check)
+            r["clocks"] = cs.summary()
             if r.get("unit") == "TFLOP/s":
                 if name == "c4" and r.get("fp8_gemm_reference_tflops"):
                     r["frac"] = r["value"] / r["fp8_gemm_reference_tflops"]
