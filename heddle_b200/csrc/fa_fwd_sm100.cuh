@@ -642,6 +642,10 @@ __global__ void __launch_bounds__(kFaThreads, 1) fa_fwd_kernel(const __grid_cons
   if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[15 * 4096 + 1] = clock64();
 #endif
 
+  // setmaxnreg.inc only hands out registers that other warpgroups of this CTA have returned with
+  // setmaxnreg.dec, so the budget has to balance or the increase waits for ever: 512 threads start with 128
+  // registers each; eight softmax warps grow by 56, four correction warps return 48 and the last four 64
+  static_assert(8 * 32 * (184 - 128) <= 4 * 32 * (128 - 80) + 4 * 32 * (128 - 64), "setmaxnreg budget does not balance");
   if (warp < 8) {
     reg_inc<184>();
     if (run) fa_softmax_role<T, D, NS>(p, s, ctx, tmem, warp >> 2);
