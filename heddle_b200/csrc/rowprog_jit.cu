@@ -118,6 +118,7 @@ struct __align__(16) Head {
   const void* in[6]; long long ld_in[6]; const void* rowvec[4]; const float* rowscalar[4];
   void* out[2]; long long ld_out[2]; long long rows; int cols;
 };
+static_assert(sizeof(Head) == 208, "must match the host's RowProgHead");
 constexpr int G = HB_G;
 constexpr int E = 8 * G;
 constexpr int THREADS = 128;

@@ -410,7 +410,8 @@ typedef struct hb_rowwise_args {
  * way); when libnvrtc cannot be loaded, the interpreter kernel.  INTERPRET: always the interpreter
  * (nothing is compiled).  COMPILED: the specialised kernel or HB_ERR_UNSUPPORTED.  All three give
  * the same results.  HEDDLE_B200_ROWWISE_JIT=0 in the environment turns the compiler off;
- * HEDDLE_B200_NVRTC names the library file to load. */
+ * HEDDLE_B200_NVRTC names the library file to load.  The first call with a new program compiles and
+ * loads a module (0.1-0.7 s) and must not be made inside a stream capture; later calls only launch. */
 typedef enum hb_rowwise_mode { HB_ROWWISE_AUTO = 0, HB_ROWWISE_INTERPRET = 1, HB_ROWWISE_COMPILED = 2 } hb_rowwise_mode;
 
 int hb_rowwise_program(const hb_rowwise_args* args);
