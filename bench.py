@@ -365,21 +365,34 @@ def strong_scaling(which: str, world: int, rank: int, dev, barrier, max_over_ran
       c2: B=4 H=32 S=4096 D=128 causal — the 128 (batch, head) units in contiguous blocks
           (``sharding.shard_batch_kvheads``);
       c3: B=8 Hq=64 Hkv=8 S=8192 D=128 causal GQA — by KV head: a rank owns Hkv/N KV heads with their
-          query heads, all batches.
+          query heads, all batches;
+      c4: FP8 e4m3 non-causal B=4 H=32 S=8192 D=128 — split like c2;
+      c5: the Llama-style layer, batch 8 x sequence 2048 — data-parallel over the batch (8 / N sequences per
+          rank, the same weights on every rank).
     Aggregate = the whole problem's algorithmic FLOPs over the slowest rank's time."""
     from heddle_b200 import ops, sharding
+
+    if which == "c5":
+        return _strong_layer(world, rank, dev, barrier, max_over_ranks, steps=min(steps, 10))
 
     gen = torch.Generator(device=dev).manual_seed(2024)
     if which == "c2":
         B, Hq, Hkv, S, D = 4, 32, 32, 4096, 128
+    elif which == "c4":
+        B, Hq, Hkv, S, D = 4, 32, 32, 8192, 128
     else:
         B, Hq, Hkv, S, D = 8, 64, 8, 8192, 128
+    causal = which != "c4"
     group = Hq // Hkv
     q = torch.randn(B, Hq, S, D, generator=gen, device=dev).to(torch.bfloat16)
     k = torch.randn(B, Hkv, S, D, generator=gen, device=dev).to(torch.bfloat16)
     v = torch.randn(B, Hkv, S, D, generator=gen, device=dev).to(torch.bfloat16)
     o = torch.empty_like(q)
-    if which == "c2":
+    scales = None
+    if which == "c4":  # per-tensor scales, e4m3 operands, bf16 output
+        scales = [float(t.abs().max()) / 448.0 for t in (q, k, v)]
+        q, k, v = ((t / s_).to(torch.float8_e4m3fn) for t, s_ in zip((q, k, v), scales))
+    if which in ("c2", "c4"):
         runs = sharding.shard_batch_kvheads(B, Hkv, world, rank)  # (batch, kv_head_start, kv_head_stop)
         if runs and all(h0 == 0 and h1 == Hkv for (_, h0, h1) in runs):
             # whole batch elements: one launch on the [b0:b1] slice
@@ -398,7 +411,10 @@ def strong_scaling(which: str, world: int, rank: int, dev, barrier, max_over_ran
 
     def step():
         for (qq, kk, vv, oo) in views:
-            ops.fa_fwd(qq, kk, vv, causal=True, out=oo)
+            if scales is None:
+                ops.fa_fwd(qq, kk, vv, causal=causal, out=oo)
+            else:
+                ops.fa_fwd(qq, kk, vv, causal=False, scales=scales, out=oo)
 
     for _ in range(3):
         step()
@@ -410,14 +426,54 @@ def strong_scaling(which: str, world: int, rank: int, dev, barrier, max_over_ran
     b_.record()
     barrier()
     ms = max_over_ranks(a.elapsed_time(b_)) / steps
-    total = 2.0 * B * Hq * S * S * D
-    pairs = units * group * (((S + 255) // 256 + 1) // 2)
+    total = (2.0 if causal else 4.0) * B * Hq * S * S * D
+    nqb = (S + 255) // 256
+    pairs = units * group * ((nqb + 1) // 2 if causal else nqb)
     res = {"value": total / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps, "scaling": "strong",
-           "problem": f"B{B}_Hq{Hq}_Hkv{Hkv}_S{S}_D{D}_causal", "split": split, "kv_units_this_rank": units,
+           "problem": f"B{B}_Hq{Hq}_Hkv{Hkv}_S{S}_D{D}_" + ("causal" if causal else "noncausal_e4m3"), "split": split,
+           "kv_units_this_rank": units,
            "launches_per_step_this_rank": len(views), "work_items_this_rank": pairs,
            "note": f"{pairs} equal-cost work items for 148 persistent CTAs on this rank"
                    + (" (less than one wave: the split, not the kernel, bounds the time)" if pairs < 148 else "")}
     del q, k, v, o
+    torch.cuda.empty_cache()
+    return res
+
+
+def _strong_layer(world: int, rank: int, dev, barrier, max_over_ranks, steps: int = 10) -> dict:
+    """Configuration 5 data-parallel over the batch: every rank holds the same layer (same seed) and runs its
+    8 / N sequences through ``torch.compile(backend=tilelang_backend)``; no collective (forward only)."""
+    from heddle_b200 import bench_configs, sharding
+    from heddle_b200.frontend import tilelang_backend
+
+    B, S, Hd = 8, 2048, 4096
+    layer = bench_configs.llama_layer()
+    gen = torch.Generator(device=dev).manual_seed(2025)
+    x = torch.randn(B, S, Hd, generator=gen, device=dev).to(torch.bfloat16)
+    b0, b1 = sharding.shard_units(B, world, rank)
+    mine = x[b0:b1]
+    ms_local = 0.0
+    if b1 > b0:
+        torch._dynamo.reset()
+        comp = torch.compile(layer, backend=tilelang_backend)
+        with torch.no_grad():
+            for _ in range(3):
+                comp(mine)
+    a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a.record()
+    if b1 > b0:
+        with torch.no_grad():
+            for _ in range(steps):
+                comp(mine)
+    b_.record()
+    barrier()
+    ms_local = a.elapsed_time(b_)
+    ms = max_over_ranks(ms_local) / steps
+    res = {"value": bench_configs.LLAMA_LAYER_FLOPS_B8_S2048 / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+           "scaling": "strong", "problem": "llama_layer_h4096_heads32_inter11008_B8_S2048", "split": "data-parallel over the batch",
+           "sequences_this_rank": b1 - b0}
+    del layer, x
     torch.cuda.empty_cache()
     return res
 
@@ -643,8 +699,7 @@ def run_ours(args):
     # ---- strong scaling: the FIXED problems of configurations 2 and 3 split over the ranks ---------
     strong = None
     if distributed and not args.kernel_only:
-        strong = {"c2": strong_scaling("c2", world, rank, dev, barrier, max_over_ranks),
-                  "c3": strong_scaling("c3", world, rank, dev, barrier, max_over_ranks)}
+        strong = {name: strong_scaling(name, world, rank, dev, barrier, max_over_ranks) for name in ("c2", "c3", "c4", "c5")}
 
     # ---- the other configurations, short runs (N = 1) ---------------------------------------------
     secondary = None

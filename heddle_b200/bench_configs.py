@@ -80,6 +80,54 @@ def _fp32_attention_check(q, k, v, out, lse, causal, heads, tol, scale=None):
         torch.backends.cuda.matmul.allow_tf32 = prev
 
 
+def llama_layer():
+    """The Llama-style decoder layer of configuration 5 (hidden 4096, 32 heads, SwiGLU 11008), weights N(0, 0.02) from
+    seed 0, bf16, on the current CUDA device."""
+    import torch.nn.functional as F
+
+    class Layer(torch.nn.Module):
+        """Pre-norm Llama block (RMSNorm eps 1e-5, rotate-half RoPE theta 10000, causal attention, SwiGLU)."""
+
+        def __init__(self, hidden=4096, heads=32, inter=11008):
+            super().__init__()
+            lin = lambda i, o: torch.nn.Linear(i, o, bias=False)
+            self.h, self.nh, self.hd = hidden, heads, hidden // heads
+            self.wq, self.wk, self.wv, self.wo = lin(hidden, hidden), lin(hidden, hidden), lin(hidden, hidden), lin(hidden, hidden)
+            self.wg, self.wu, self.wd = lin(hidden, inter), lin(hidden, inter), lin(inter, hidden)
+            self.g1, self.g2 = torch.nn.Parameter(torch.ones(hidden)), torch.nn.Parameter(torch.ones(hidden))
+
+        def rms(self, x, g):
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * g
+
+        def rope(self, x, cos, sin):
+            d = self.hd // 2
+            x1, x2 = x[..., :d], x[..., d:]
+            return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+        def forward(self, x):
+            B, S, _ = x.shape
+            h = self.rms(x, self.g1)
+            q, k, v = (w(h).view(B, S, self.nh, self.hd).transpose(1, 2) for w in (self.wq, self.wk, self.wv))
+            inv = 1.0 / (10000.0 ** (torch.arange(0, self.hd, 2, dtype=torch.float32, device=x.device) / self.hd))
+            ang = torch.arange(S, dtype=torch.float32, device=x.device)[:, None] * inv[None, :]
+            cos, sin = torch.cos(ang).to(x.dtype), torch.sin(ang).to(x.dtype)
+            a = F.scaled_dot_product_attention(self.rope(q, cos, sin), self.rope(k, cos, sin), v, is_causal=True)
+            x = x + self.wo(a.transpose(1, 2).reshape(B, S, self.h))
+            h = self.rms(x, self.g2)
+            return x + self.wd(F.silu(self.wg(h)) * self.wu(h))
+
+    torch.manual_seed(0)
+    layer = Layer()
+    with torch.no_grad():
+        for prm in layer.parameters():
+            if prm.dim() == 2:
+                prm.normal_(0.0, 0.02)
+    return layer.to(torch.bfloat16).cuda()
+
+
+LLAMA_LAYER_FLOPS_B8_S2048 = 6.907e12  # algorithmic FLOPs of the layer at batch 8, sequence 2048
+
+
 def run_config(name: str, steps: int = 20, warmup: int = 3, check: bool = False) -> dict:
     """Time one secondary configuration; returns its JSON-able record."""
     import types
@@ -255,55 +303,16 @@ def run_config(name: str, steps: int = 20, warmup: int = 3, check: bool = False)
         flops = 2.0 * M * N * K
         line.update(workload="swiglu_gemm_M16384_N22016_K4096", dtype="bf16")
     else:
-        import torch.nn.functional as F
-
         from .frontend import tilelang_backend
 
-        class Layer(torch.nn.Module):
-            """Pre-norm Llama block (RMSNorm eps 1e-5, rotate-half RoPE theta 10000, causal attention, SwiGLU)."""
-
-            def __init__(self, hidden=4096, heads=32, inter=11008):
-                super().__init__()
-                lin = lambda i, o: torch.nn.Linear(i, o, bias=False)
-                self.h, self.nh, self.hd = hidden, heads, hidden // heads
-                self.wq, self.wk, self.wv, self.wo = lin(hidden, hidden), lin(hidden, hidden), lin(hidden, hidden), lin(hidden, hidden)
-                self.wg, self.wu, self.wd = lin(hidden, inter), lin(hidden, inter), lin(inter, hidden)
-                self.g1, self.g2 = torch.nn.Parameter(torch.ones(hidden)), torch.nn.Parameter(torch.ones(hidden))
-
-            def rms(self, x, g):
-                return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * g
-
-            def rope(self, x, cos, sin):
-                d = self.hd // 2
-                x1, x2 = x[..., :d], x[..., d:]
-                return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
-
-            def forward(self, x):
-                B, S, _ = x.shape
-                h = self.rms(x, self.g1)
-                q, k, v = (w(h).view(B, S, self.nh, self.hd).transpose(1, 2) for w in (self.wq, self.wk, self.wv))
-                inv = 1.0 / (10000.0 ** (torch.arange(0, self.hd, 2, dtype=torch.float32, device=x.device) / self.hd))
-                ang = torch.arange(S, dtype=torch.float32, device=x.device)[:, None] * inv[None, :]
-                cos, sin = torch.cos(ang).to(x.dtype), torch.sin(ang).to(x.dtype)
-                a = F.scaled_dot_product_attention(self.rope(q, cos, sin), self.rope(k, cos, sin), v, is_causal=True)
-                x = x + self.wo(a.transpose(1, 2).reshape(B, S, self.h))
-                h = self.rms(x, self.g2)
-                return x + self.wd(F.silu(self.wg(h)) * self.wu(h))
-
-        torch.manual_seed(0)
-        layer = Layer()
-        with torch.no_grad():
-            for prm in layer.parameters():
-                if prm.dim() == 2:
-                    prm.normal_(0.0, 0.02)
-        layer = layer.to(torch.bfloat16).cuda()
+        layer = llama_layer()
         x = rnd(8, 2048, 4096).bfloat16()
         with torch.no_grad():
             eager_ms = _time(lambda: layer(x), args.steps, args.warmup)
             torch._dynamo.reset()
             comp = torch.compile(layer, backend=tilelang_backend)
             ms = _time(lambda: comp(x), args.steps, args.warmup)
-        flops = 6.907e12
+        flops = LLAMA_LAYER_FLOPS_B8_S2048
         line.update(workload="llama_layer_h4096_heads32_inter11008_B8_S2048", dtype="bf16", eager_pytorch_ms=eager_ms,
                     eager_pytorch_tflops=flops / eager_ms / 1e9)
         if check:
