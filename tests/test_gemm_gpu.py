@@ -323,3 +323,24 @@ def test_cta_pairs_and_single_cta_kernels_agree_bitwise(ops):
         assert ops.status_word() == 0
     finally:
         ops.set_gemm_schedule(prev)
+
+
+def test_full_size_projection_by_size_independent_properties(ops):
+    """16384 x 4096 x 4096 (the layer's O projection): sampled rows against fp32, the row sums against
+    a @ (w^T 1) (a checksum of checksums), and exact linearity in the activation (x2 is exact in bf16)."""
+    g = torch.Generator(device="cuda").manual_seed(41)
+    M, N, K = 16384, 4096, 4096
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    out = ops.gemm_epilogue(a, w)
+    assert ops.status_word() == 0
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, 8191, 8192, 16383], device="cuda")
+    ref = a[rows].float() @ w.float().t()
+    assert float((out[rows].float() - ref).abs().max()) <= 1e-2 * max(1.0, float(ref.abs().max()))
+    # sum over the 4096 outputs of a row: rounding errors of the bf16 results add up like a random walk
+    checksum = a.float() @ w.float().sum(dim=0)
+    got = out.float().sum(dim=1)
+    bound = 64.0 * 2.0 ** -9 * out.float().abs().max() + 1e-3 * checksum.abs().max()
+    assert float((got - checksum).abs().max()) <= float(bound)
+    twice = ops.gemm_epilogue(a * 2, w)
+    assert torch.equal(twice, out * 2)
