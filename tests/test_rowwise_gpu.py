@@ -152,3 +152,27 @@ def test_compiled_modules_run_their_partitions_on_the_kernel(ops):
     assert seen and seen[0].count(fusion.hb_rowwise) == 2 and seen[0].count(fusion.hb_linear) == 2
     err = (got.float() - want).abs().max().item()
     assert err <= 2e-2 * max(1.0, want.abs().max().item()), err
+
+
+def test_full_size_programs_by_size_independent_properties(ops):
+    """32768 x 4096 bf16 (the bench configuration): exact doubling, a softmax program whose rows sum to one,
+    and a sampled block against the CPU oracle."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(32768, 4096, generator=g, device="cuda").to(torch.bfloat16)
+    y = torch.randn(32768, 4096, generator=g, device="cuda").to(torch.bfloat16)
+    double = (("load", "input", 0, 0.0), ("mul", "imm", 0, 2.0), ("store_out", None, 0, 0.0))
+    assert torch.equal(ops.rowwise_program(double, [x]), x * 2)
+    chain = (("load", "input", 0, 0.0), ("silu", None, 0, 0.0), ("mul", "input", 1, 0.0), ("add", "imm", 0, 1.5),
+             ("store_out", None, 0, 0.0))
+    out = ops.rowwise_program(chain, [x, y])
+    rows = slice(20000, 20064)
+    _close(out[rows], run_program(chain, [x[rows].cpu(), y[rows].cpu()]))
+    softmax = (("load", "input", 0, 0.0), ("reduce_max", None, 0, 0.0), ("sub", "reduced", 0, 0.0), ("exp", None, 0, 0.0),
+               ("store_tmp", None, 0, 0.0), ("reduce_sum", None, 1, 0.0), ("load", "tmp", 0, 0.0), ("div", "reduced", 1, 0.0),
+               ("store_out", None, 0, 0.0))
+    p = ops.rowwise_program(softmax, [x])
+    sums = p.float().sum(dim=1)
+    assert float((sums - 1.0).abs().max()) <= 4e-3      # 4096 bf16 roundings of values that sum to one
+    assert float(p.float().min()) >= 0.0
+    _close(p[rows], run_program(softmax, [x[rows].cpu()]), ulps=3.0)
+    assert ops.status_word() == 0
